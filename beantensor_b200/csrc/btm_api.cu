@@ -1,0 +1,442 @@
+// C ABI of libbtm.so: argument checks, per-device state, tensor-map encoding and dispatch to the
+// kernels. Nothing here computes on the CPU; every path ends in a CUDA launch or an error.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "btm_internal.h"
+
+namespace btm {
+
+static thread_local char g_err[512] = "";
+static thread_local int g_code = BTM_OK;
+static int last_code() { return g_code != BTM_OK ? g_code : BTM_ERR_CUDA; }
+
+int set_error(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    g_code = code;
+    return code;
+}
+
+int check_cuda(cudaError_t e, const char *what)
+{
+    if (e == cudaSuccess) return BTM_OK;
+    // Same split as the reference's CUDA_CHECK_ERROR (Errors/Logic.h:50-59): allocation
+    // failures are reported apart from every other runtime error.
+    if (e == cudaErrorMemoryAllocation) return set_error(BTM_ERR_OOM, "CUDA Error: %s (%s)", cudaGetErrorString(e), what);
+    return set_error(BTM_ERR_CUDA, "CUDA Error: %s (%s)", cudaGetErrorString(e), what);
+}
+
+constexpr int kMaxDevices = 64;
+static DeviceState g_dev[kMaxDevices];
+static std::mutex g_dev_mu;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+DeviceState *device_state(int device)
+{
+    if (device < 0 || device >= kMaxDevices) {
+        set_error(BTM_ERR_INVALID, "Invalid GPU ID %d", device);
+        return nullptr;
+    }
+    int count = 0;
+    if (check_cuda(cudaGetDeviceCount(&count), "cudaGetDeviceCount")) return nullptr;
+    if (device >= count) {
+        set_error(BTM_ERR_INVALID, "Invalid GPU ID %d (device count %d)", device, count);
+        return nullptr;
+    }
+    if (check_cuda(cudaSetDevice(device), "cudaSetDevice")) return nullptr;
+    DeviceState *ds = &g_dev[device];
+    std::lock_guard<std::mutex> lock(g_dev_mu);
+    if (ds->ready) return ds;
+    cudaDeviceProp prop;
+    if (check_cuda(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties")) return nullptr;
+    if (prop.major != 10) {
+        set_error(BTM_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
+                  prop.minor);
+        return nullptr;
+    }
+    if (!g_encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint"))
+            return nullptr;
+        if (qres != cudaDriverEntryPointSuccess || !fn) {
+            set_error(BTM_ERR_CUDA, "CUDA Error: driver does not export cuTensorMapEncodeTiled");
+            return nullptr;
+        }
+        g_encode = (EncodeTiledFn)fn;
+    }
+    if (check_cuda(cudaMalloc(&ds->status, sizeof(int)), "cudaMalloc(status)")) return nullptr;
+    if (check_cuda(cudaMemset(ds->status, 0, sizeof(int)), "cudaMemset(status)")) return nullptr;
+    if (configure_gemm_tc_kernels()) return nullptr;
+    ds->sm_count = prop.multiProcessorCount;
+    ds->ws = nullptr;
+    ds->ws_bytes = 0;
+    ds->ready = true;
+    return ds;
+}
+
+int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
+                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1)
+{
+    CUtensorMapDataType dt = dtype == BTM_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                             : dtype == BTM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    cuuint32_t box[3] = {box0, box1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(out, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return set_error(BTM_ERR_CUDA, "CUDA Error: cuTensorMapEncodeTiled failed with code %d (dims %llu x %llu x %llu)", (int)r,
+                         (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2);
+    return BTM_OK;
+}
+
+static size_t es_of(int dtype) { return dtype == BTM_F32 ? 4 : 2; }
+static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+// Can TMA address this operand? Base and every pitch must be multiples of 16 bytes.
+static bool tma_ok(const void *p, long long ld, long long stride, int batch, size_t es)
+{
+    if (!aligned16(p)) return false;
+    if ((ld * (long long)es) % 16) return false;
+    if (batch > 1 && (stride * (long long)es) % 16) return false;
+    return true;
+}
+
+struct GemmCall {
+    int dtype, batch, M, N, K;
+    const void *A, *B;
+    long long lda, ldb, strideA, strideB;
+    void *C[kMaxDst];
+    int ndst;
+    long long ldc, strideC, col0;
+};
+
+static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
+{
+    const size_t es = 2;
+    const bool tc = c.K > 0 && tma_ok(c.A, c.lda, c.strideA, c.batch, es) && tma_ok(c.B, c.ldb, c.strideB, c.batch, es);
+    if (!tc) {
+        for (int d = 0; d < c.ndst; ++d) {
+            int rc = launch_gemm_simt(c.dtype, st, c.batch, c.M, c.N, c.K, c.A, c.lda, c.strideA, c.B, c.ldb, c.strideB,
+                                      (char *)c.C[d] + c.col0 * (long long)es, c.ldc, c.strideC);
+            if (rc) return rc;
+        }
+        return BTM_OK;
+    }
+    CUtensorMap tmA, tmB;
+    const uint64_t sA = c.batch > 1 ? (uint64_t)c.strideA * es : (uint64_t)c.lda * es;
+    const uint64_t sB = c.batch > 1 ? (uint64_t)c.strideB * es : (uint64_t)c.ldb * es;
+    int rc = encode_tmap_3d(&tmA, c.dtype, c.A, (uint64_t)c.K, (uint64_t)c.M, (uint64_t)c.batch, (uint64_t)c.lda * es, sA, 64, 128);
+    if (rc) return rc;
+    rc = encode_tmap_3d(&tmB, c.dtype, c.B, (uint64_t)c.N, (uint64_t)c.K, (uint64_t)c.batch, (uint64_t)c.ldb * es, sB, 64, 64);
+    if (rc) return rc;
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = c.M;
+    p.N = c.N;
+    p.K = c.K;
+    p.batch = c.batch;
+    p.group_m = 8;
+    p.ndst = c.ndst;
+    bool vec = (c.ldc * (long long)es) % 16 == 0 && (c.col0 * (long long)es) % 16 == 0 &&
+               (c.batch == 1 || (c.strideC * (long long)es) % 16 == 0);
+    for (int d = 0; d < c.ndst; ++d) {
+        p.C[d] = c.C[d];
+        vec = vec && aligned16(c.C[d]);
+    }
+    p.ldc = c.ldc;
+    p.strideC = c.strideC;
+    p.col0 = c.col0;
+    p.c_vec_ok = vec ? 1 : 0;
+    p.status = ds->status;
+    return launch_gemm_tc(c.dtype, st, ds->sm_count, tmA, tmB, p, 0);
+}
+
+static int run_f32(DeviceState *ds, cudaStream_t st, const GemmCall &c, void *ws, size_t ws_bytes)
+{
+    // Operand planes in scratch: A_hi, A_lo [M, Kp] then B^T_hi, B^T_lo [N, Kp], pitch padded to 4 floats.
+    const long long Kp = (c.K + 3) & ~3LL;
+    const size_t a_plane = (size_t)c.M * Kp, b_plane = (size_t)c.N * Kp;
+    const size_t need = (2 * a_plane + 2 * b_plane) * sizeof(float);
+    if (c.K == 0 || c.M == 0 || c.N == 0)
+        return launch_gemm_simt(BTM_F32, st, 1, c.M, c.N, c.K, c.A, c.lda, 0, c.B, c.ldb, 0, c.C[0], c.ldc, 0);
+    if (ws_bytes < need) return set_error(BTM_ERR_INVALID, "fp32 matmul: workspace of %zu bytes is smaller than the %zu needed", ws_bytes, need);
+    float *a_hi = (float *)ws, *a_lo = a_hi + a_plane, *b_hi = a_lo + a_plane, *b_lo = b_hi + b_plane;
+    int rc = launch_split_tf32(st, (const float *)c.A, c.lda, c.M, c.K, a_hi, a_lo, Kp);
+    if (rc) return rc;
+    rc = launch_split_tf32_transpose(st, (const float *)c.B, c.ldb, c.K, c.N, b_hi, b_lo, Kp);
+    if (rc) return rc;
+    // The B box is one whole tile (bn rows), so the tile width is chosen here: 128 columns, or 64
+    // when that leaves SMs without a tile.
+    const long long t128 = (long long)((c.M + 127) / 128) * ((c.N + 127) / 128);
+    const int bn = t128 < ds->sm_count ? 64 : 128;
+    CUtensorMap tmA, tmB;
+    rc = encode_tmap_3d(&tmA, BTM_F32, a_hi, (uint64_t)c.K, (uint64_t)c.M, 2, (uint64_t)Kp * 4, (uint64_t)a_plane * 4, 32, 128);
+    if (rc) return rc;
+    rc = encode_tmap_3d(&tmB, BTM_F32, b_hi, (uint64_t)c.K, (uint64_t)c.N, 2, (uint64_t)Kp * 4, (uint64_t)b_plane * 4, 32, bn);
+    if (rc) return rc;
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = c.M;
+    p.N = c.N;
+    p.K = c.K;
+    p.batch = 1;
+    p.group_m = 8;
+    p.ndst = 1;
+    p.C[0] = c.C[0];
+    p.ldc = c.ldc;
+    p.c_vec_ok = (aligned16(c.C[0]) && (c.ldc * 4) % 16 == 0) ? 1 : 0;
+    p.status = ds->status;
+    return launch_gemm_tc(BTM_F32, st, ds->sm_count, tmA, tmB, p, bn);
+}
+
+static int check_gemm_args(int dtype, int M, int N, int K, const void *A, long long lda, const void *B, long long ldb,
+                           const void *C, long long ldc)
+{
+    if (dtype != BTM_F16 && dtype != BTM_BF16 && dtype != BTM_F32)
+        return set_error(BTM_ERR_UNSUPPORTED, "matmul: dtype %d is not supported (Float16, BFloat16, Float32 only)", dtype);
+    if (M < 0 || N < 0 || K < 0) return set_error(BTM_ERR_INVALID, "matmul: negative dimension (M=%d N=%d K=%d)", M, N, K);
+    if (M > 0 && N > 0 && !C) return set_error(BTM_ERR_INVALID, "matmul: null output pointer");
+    if (M > 0 && K > 0 && !A) return set_error(BTM_ERR_INVALID, "matmul: null A pointer");
+    if (K > 0 && N > 0 && !B) return set_error(BTM_ERR_INVALID, "matmul: null B pointer");
+    if (lda < K || ldb < N || ldc < N)
+        return set_error(BTM_ERR_INVALID, "matmul: leading dimension too small (lda=%lld ldb=%lld ldc=%lld for K=%d N=%d)", lda, ldb, ldc, K, N);
+    const size_t es = es_of(dtype);
+    if (((uintptr_t)A % es) || ((uintptr_t)B % es) || ((uintptr_t)C % es))
+        return set_error(BTM_ERR_INVALID, "matmul: pointer not aligned to the element size");
+    return BTM_OK;
+}
+
+} // namespace btm
+
+using namespace btm;
+
+extern "C" {
+
+size_t btm_dtype_size(int dtype)
+{
+    switch (dtype) {
+    case BTM_BF16: case BTM_F16: case BTM_I16: case BTM_U16: return 2;
+    case BTM_F32: case BTM_I32: case BTM_U32: return 4;
+    case BTM_F64: case BTM_I64: case BTM_U64: return 8;
+    case BTM_I8: case BTM_U8: case BTM_INT4X2: return 1;
+    default: return 0;
+    }
+}
+
+int btm_version(void) { return 100; }
+
+const char *btm_last_error_string(void) { return g_err; }
+
+int btm_init(int device) { return device_state(device) ? BTM_OK : last_code(); }
+
+int btm_check_device_status(int device, void *stream)
+{
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    cudaStream_t st = (cudaStream_t)stream;
+    int host = 0;
+    int rc = check_cuda(cudaMemcpyAsync(&host, ds->status, sizeof(int), cudaMemcpyDeviceToHost, st), "status readback");
+    if (rc) return rc;
+    rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+    if (rc) return rc;
+    if (host != 0) {
+        cudaMemsetAsync(ds->status, 0, sizeof(int), st);
+        cudaStreamSynchronize(st);
+        return set_error(BTM_ERR_TIMEOUT, "CUDA Error: a kernel wait ran out (device status %d)", host);
+    }
+    return BTM_OK;
+}
+
+int btm_gemm(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B, int64_t ldb,
+             void *C, int64_t ldc)
+{
+    int rc = check_gemm_args(dtype, M, N, K, A, lda, B, ldb, C, ldc);
+    if (rc) return rc;
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    if (M == 0 || N == 0) return BTM_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    GemmCall c;
+    memset(&c, 0, sizeof(c));
+    c.dtype = dtype; c.batch = 1; c.M = M; c.N = N; c.K = K;
+    c.A = A; c.B = B; c.lda = lda; c.ldb = ldb;
+    c.C[0] = C; c.ndst = 1; c.ldc = ldc;
+    if (dtype != BTM_F32) return run_16bit(ds, st, c);
+    const size_t need = btm_gemm_f32_workspace_bytes(M, N, K);
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mu);
+        if (ds->ws_bytes < need) {
+            // Growing the scratch must not pull memory from under work already queued.
+            rc = check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+            if (rc) return rc;
+            if (ds->ws) cudaFree(ds->ws);
+            ds->ws = nullptr;
+            ds->ws_bytes = 0;
+            rc = check_cuda(cudaMalloc(&ds->ws, need), "cudaMalloc(fp32 split scratch)");
+            if (rc) return rc;
+            ds->ws_bytes = need;
+        }
+    }
+    return run_f32(ds, st, c, ds->ws, ds->ws_bytes);
+}
+
+size_t btm_gemm_f32_workspace_bytes(int M, int N, int K)
+{
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const size_t Kp = ((size_t)K + 3) & ~(size_t)3;
+    return (2 * (size_t)M * Kp + 2 * (size_t)N * Kp) * sizeof(float);
+}
+
+int btm_gemm_f32_ws(int device, void *stream, int M, int N, int K, const void *A, int64_t lda, const void *B, int64_t ldb,
+                    void *C, int64_t ldc, void *workspace, size_t workspace_bytes)
+{
+    int rc = check_gemm_args(BTM_F32, M, N, K, A, lda, B, ldb, C, ldc);
+    if (rc) return rc;
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    if (M == 0 || N == 0) return BTM_OK;
+    if (K > 0 && (!workspace || ((uintptr_t)workspace & 255)))
+        return set_error(BTM_ERR_INVALID, "fp32 matmul: workspace must be non-null and 256-byte aligned");
+    GemmCall c;
+    memset(&c, 0, sizeof(c));
+    c.dtype = BTM_F32; c.batch = 1; c.M = M; c.N = N; c.K = K;
+    c.A = A; c.B = B; c.lda = lda; c.ldb = ldb;
+    c.C[0] = C; c.ndst = 1; c.ldc = ldc;
+    return run_f32(ds, (cudaStream_t)stream, c, workspace, workspace_bytes);
+}
+
+int btm_bmm(int device, void *stream, int dtype, int batch, int M, int N, int K, const void *A, int64_t strideA,
+            const void *B, int64_t strideB, void *C, int64_t strideC)
+{
+    if (dtype != BTM_F16 && dtype != BTM_BF16)
+        return set_error(BTM_ERR_UNSUPPORTED, "batched matmul: dtype %d is not supported (Float16, BFloat16 only)", dtype);
+    if (batch < 0) return set_error(BTM_ERR_INVALID, "batched matmul: negative batch");
+    int rc = check_gemm_args(dtype, M, N, K, A, K, B, N, C, N);
+    if (rc) return rc;
+    if (batch > 1 && (strideA < (int64_t)M * K || strideB < (int64_t)K * N || strideC < (int64_t)M * N))
+        return set_error(BTM_ERR_INVALID, "batched matmul: batch stride smaller than one matrix");
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    if (batch == 0 || M == 0 || N == 0) return BTM_OK;
+    GemmCall c;
+    memset(&c, 0, sizeof(c));
+    c.dtype = dtype; c.batch = batch; c.M = M; c.N = N; c.K = K;
+    c.A = A; c.B = B; c.lda = K; c.ldb = N; c.strideA = strideA; c.strideB = strideB;
+    c.C[0] = C; c.ndst = 1; c.ldc = N; c.strideC = strideC;
+    return run_16bit(ds, (cudaStream_t)stream, c);
+}
+
+int btm_gemm_nshard(int device, void *stream, int dtype, int M, int Nloc, int K, const void *A, int64_t lda,
+                    const void *B_local, int64_t ldb, void *const *C_ranks, int64_t ldc, int rank, int nranks)
+{
+    if (dtype != BTM_F16 && dtype != BTM_BF16)
+        return set_error(BTM_ERR_UNSUPPORTED, "sharded matmul: dtype %d is not supported (Float16, BFloat16 only)", dtype);
+    if (nranks < 1 || nranks > kMaxDst || rank < 0 || rank >= nranks)
+        return set_error(BTM_ERR_INVALID, "sharded matmul: rank %d of %d is out of range (at most %d ranks)", rank, nranks, kMaxDst);
+    if (!C_ranks) return set_error(BTM_ERR_INVALID, "sharded matmul: null destination table");
+    if (ldc < (int64_t)Nloc * nranks) return set_error(BTM_ERR_INVALID, "sharded matmul: ldc=%lld is smaller than nranks*Nloc", (long long)ldc);
+    for (int r = 0; r < nranks; ++r)
+        if (!C_ranks[r] && M > 0 && Nloc > 0) return set_error(BTM_ERR_INVALID, "sharded matmul: null C for rank %d", r);
+    int rc = check_gemm_args(dtype, M, Nloc, K, A, lda, B_local, ldb, C_ranks[rank], ldc);
+    if (rc) return rc;
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    if (M == 0 || Nloc == 0) return BTM_OK;
+    GemmCall c;
+    memset(&c, 0, sizeof(c));
+    c.dtype = dtype; c.batch = 1; c.M = M; c.N = Nloc; c.K = K;
+    c.A = A; c.B = B_local; c.lda = lda; c.ldb = ldb;
+    // Local copy first, then the peers starting from the next rank so that the ranks do not
+    // all write into the same peer at the same moment.
+    c.C[0] = C_ranks[rank];
+    for (int i = 1; i < nranks; ++i) c.C[i] = C_ranks[(rank + i) % nranks];
+    c.ndst = nranks; c.ldc = ldc; c.col0 = (long long)rank * Nloc;
+    return run_16bit(ds, (cudaStream_t)stream, c);
+}
+
+int btm_int4_matmul(int device, void *stream, int M, int N, int K, int group, const void *act_f16, const void *w_packed,
+                    const void *scales_f16, void *out_f16)
+{
+    if (M < 0 || N < 0 || K < 0) return set_error(BTM_ERR_INVALID, "int4 matmul: negative dimension");
+    if (group <= 0 || K % 2 || (K % group) != 0) return set_error(BTM_ERR_INVALID, "int4 matmul: K=%d must be even and a multiple of group=%d", K, group);
+    if (M > 0 && N > 0 && (!out_f16 || (K > 0 && (!act_f16 || !w_packed || !scales_f16))))
+        return set_error(BTM_ERR_INVALID, "int4 matmul: null pointer");
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    return launch_int4_gemv((cudaStream_t)stream, ds->sm_count, M, N, K, group, act_f16, w_packed, scales_f16, out_f16);
+}
+
+int btm_int4_dequant(int device, void *stream, int N, int K, int group, const void *w_packed, const void *scales_f16,
+                     void *out_f16)
+{
+    if (N < 0 || K < 0) return set_error(BTM_ERR_INVALID, "int4 dequant: negative dimension");
+    if (group <= 0 || K % 2 || (K % group) != 0) return set_error(BTM_ERR_INVALID, "int4 dequant: K=%d must be even and a multiple of group=%d", K, group);
+    if ((long long)N * K > 0 && (!w_packed || !scales_f16 || !out_f16)) return set_error(BTM_ERR_INVALID, "int4 dequant: null pointer");
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    return launch_int4_dequant((cudaStream_t)stream, N, K, group, w_packed, scales_f16, out_f16);
+}
+
+int btm_int4_unpack(int device, void *stream, int N, int K, const void *w_packed, void *out_i8)
+{
+    if (N < 0 || K < 0 || K % 2) return set_error(BTM_ERR_INVALID, "int4 unpack: K=%d must be even and dimensions non-negative", K);
+    if ((long long)N * K > 0 && (!w_packed || !out_i8)) return set_error(BTM_ERR_INVALID, "int4 unpack: null pointer");
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    return launch_int4_unpack((cudaStream_t)stream, N, K, w_packed, out_i8);
+}
+
+int btm_ipc_alloc(int device, size_t bytes, void **ptr, unsigned char handle[64])
+{
+    if (!ptr || !handle || bytes == 0) return set_error(BTM_ERR_INVALID, "ipc alloc: bad arguments");
+    if (!device_state(device)) return last_code();
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    int rc = check_cuda(cudaMalloc(ptr, bytes), "cudaMalloc(ipc)");
+    if (rc) return rc;
+    cudaIpcMemHandle_t h;
+    rc = check_cuda(cudaIpcGetMemHandle(&h, *ptr), "cudaIpcGetMemHandle");
+    if (rc) {
+        cudaFree(*ptr);
+        *ptr = nullptr;
+        return rc;
+    }
+    memcpy(handle, &h, 64);
+    return BTM_OK;
+}
+
+int btm_ipc_open(int device, const unsigned char handle[64], void **ptr)
+{
+    if (!ptr || !handle) return set_error(BTM_ERR_INVALID, "ipc open: bad arguments");
+    if (!device_state(device)) return last_code();
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    return check_cuda(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+}
+
+int btm_ipc_close(int device, void *ptr)
+{
+    if (!device_state(device)) return last_code();
+    return check_cuda(cudaIpcCloseMemHandle(ptr), "cudaIpcCloseMemHandle");
+}
+
+int btm_ipc_free(int device, void *ptr)
+{
+    if (!device_state(device)) return last_code();
+    return check_cuda(cudaFree(ptr), "cudaFree(ipc)");
+}
+
+} // extern "C"

@@ -1,0 +1,62 @@
+// Internal declarations shared by the translation units of libbtm.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/btm.h"
+
+namespace btm {
+
+constexpr int kMaxDst = 8; // destinations of one epilogue store (ranks of a single NVSwitch box)
+
+// Per-call description of a (batched) matmul for the tensor-core kernels.
+struct GemmParams {
+    int M, N, K;         // one product
+    int batch;           // independent products (1 for plain matmul)
+    int tiles_m, tiles_n; // tiles per product
+    int num_kb;          // k-blocks per tile
+    int group_m;         // tile raster: m-tiles per L2 group
+    void *C[kMaxDst];    // output bases; [0] is local, others are peer-mapped copies of C
+    int ndst;
+    long long ldc;     // elements
+    long long strideC; // elements between products
+    long long col0;    // first output column of this launch inside C
+    int c_vec_ok;      // 16-byte vector stores into C are legal
+    int *status;       // device status word (bounded waits report here)
+};
+
+// Per-device state, created once by btm_init.
+struct DeviceState {
+    bool ready;
+    int sm_count;
+    int *status; // device memory, one int
+    void *ws;    // library-owned scratch for the fp32 split
+    size_t ws_bytes;
+};
+
+int set_error(int code, const char *fmt, ...);
+int check_cuda(cudaError_t e, const char *what);
+DeviceState *device_state(int device); // NULL + error set on failure
+
+// Encodes a rank-3 tiled tensor map with 128-byte swizzle (dims innermost first).
+int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
+                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1);
+
+// Launchers (defined next to their kernels). All return a btm_status.
+int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB,
+                   const GemmParams &p, int force_bn);
+int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K, const void *A, long long lda,
+                     long long strideA, const void *B, long long ldb, long long strideB, void *C, long long ldc,
+                     long long strideC);
+int launch_split_tf32(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
+                      float *dst_lo, long long ld_dst);
+int launch_split_tf32_transpose(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
+                                float *dst_lo, long long ld_dst);
+int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act,
+                     const void *w, const void *scales, void *out);
+int launch_int4_dequant(cudaStream_t st, int N, int K, int group, const void *w, const void *scales, void *out);
+int launch_int4_unpack(cudaStream_t st, int N, int K, const void *w, void *out);
+int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once per device
+
+} // namespace btm

@@ -1,0 +1,428 @@
+// Tensor-core matmul for sm_100a: C[M,N] = A[M,K] . B[K,N], row-major, fp32 accumulation.
+//
+// One persistent CTA per SM walks a static list of 128 x BN output tiles (all products of a
+// batched call share one list). Inside a CTA the work is split by warp:
+//   warp 0      TMA producer: streams 128-byte-wide k-slices of A and B into a ring of
+//               shared-memory stages (128-byte swizzle), one mbarrier per stage;
+//   warp 1      owns tensor memory and issues tcgen05.mma (one elected lane); accumulators
+//               live in tensor memory, two of them, so the epilogue of tile i overlaps the
+//               main loop of tile i+1;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (one 32-row quadrant per warp), round to
+//               the output type and store to C — to every destination when the call carries
+//               peer copies of C (the fused all-gather of the N-sharded product).
+// A is K-major in shared memory. B is row-major [K,N] in global memory, so it is loaded as
+// N-contiguous 128-byte chunks and consumed as an MN-major operand; no transpose pass exists.
+// fp32 inputs run as a three-term TF32 split: z = 0/1 of the tensor maps select the hi and lo
+// planes prepared by split_tf32_kernel and each k-step issues hi.hi, hi.lo and lo.hi.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "btm_internal.h"
+#include "btm_ptx.cuh"
+
+namespace btm {
+
+constexpr int BM = 128;          // rows of one output tile = accumulator lanes
+constexpr int SLICE_BYTES = 128; // bytes of K (for A) or N (for B) per shared-memory row = swizzle span
+constexpr int UMMA_K_BYTES = 32; // bytes of K consumed by one tcgen05.mma
+constexpr int NUM_THREADS = 192;
+
+template <int BN, int DT>
+struct TileCfg {
+    static constexpr bool kTf32 = (DT == BTM_F32);
+    static constexpr int kEs = kTf32 ? 4 : 2;              // element bytes
+    static constexpr int kBKE = SLICE_BYTES / kEs;          // k elements per stage
+    static constexpr int kPlanes = kTf32 ? 2 : 1;           // hi/lo planes
+    // 16-bit B stays row-major [K,N] in global memory and is consumed MN-major: BN/64 chunks of
+    // kBKE rows x 128 B. The fp32 planes are written transposed ([N,K]) by the split pass, so B
+    // is K-major like A: BN rows x 128 B from a single TMA box.
+    static constexpr bool kBMnMajor = !kTf32;
+    static constexpr int kChunkN = SLICE_BYTES / kEs;       // n elements per MN-major B chunk
+    static constexpr int kChunks = BN / kChunkN;            // MN-major B chunks per stage
+    static constexpr int kChunkBytes = kBKE * SLICE_BYTES;  // one MN-major chunk: kBKE rows of 128 B
+    static constexpr int kABytes = BM * SLICE_BYTES;        // one A plane
+    static constexpr int kBBytes = BN * SLICE_BYTES;        // one B plane (either major)
+    static constexpr int kStageBytes = kPlanes * (kABytes + kBBytes);
+    static constexpr int kStages = (kStageBytes <= 48 * 1024) ? 4 : 3;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024; // + alignment slack
+    static constexpr int kTmemCols = 2 * BN;                // two accumulators
+    static constexpr int kKSteps = SLICE_BYTES / UMMA_K_BYTES;
+    static constexpr int kUmmaKRows = UMMA_K_BYTES / kEs;   // k rows of B per mma
+    static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "tensor memory columns must be a power of two");
+};
+
+struct TileCoord {
+    int b, m, n;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int tile)
+{
+    const int per_batch = p.tiles_m * p.tiles_n;
+    TileCoord c;
+    c.b = tile / per_batch;
+    const int t = tile - c.b * per_batch;
+    const int per_group = p.group_m * p.tiles_n;
+    const int gid = t / per_group;
+    const int first_m = gid * p.group_m;
+    const int gsz = min(p.tiles_m - first_m, p.group_m);
+    const int r = t - gid * per_group;
+    c.m = first_m + r % gsz;
+    c.n = r / gsz;
+    return c;
+}
+
+template <int DT>
+__device__ __forceinline__ void store_row_chunk(const GemmParams &p, const uint32_t (&acc)[32], long long elem_off,
+                                                int ncols_valid)
+{
+    // acc holds 32 consecutive fp32 columns of one output row; elem_off is the element offset
+    // of the first of them inside C. ncols_valid <= 32 trims the right edge of the matrix.
+    if constexpr (DT == BTM_F32) {
+        if (ncols_valid == 32 && p.c_vec_ok) {
+#pragma unroll
+            for (int d = 0; d < kMaxDst; ++d) {
+                if (d >= p.ndst) break;
+                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<float *>(p.C[d]) + elem_off);
+#pragma unroll
+                for (int v = 0; v < 8; ++v) dst[v] = make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+            }
+        } else {
+            for (int d = 0; d < p.ndst; ++d) {
+                float *dst = reinterpret_cast<float *>(p.C[d]) + elem_off;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < ncols_valid) dst[j] = __uint_as_float(acc[j]);
+            }
+        }
+    } else {
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float lo = __uint_as_float(acc[2 * j]), hi = __uint_as_float(acc[2 * j + 1]);
+            if constexpr (DT == BTM_F16) {
+                __half2 h = __floats2half2_rn(lo, hi);
+                packed[j] = *reinterpret_cast<uint32_t *>(&h);
+            } else {
+                __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                packed[j] = *reinterpret_cast<uint32_t *>(&h);
+            }
+        }
+        if (ncols_valid == 32 && p.c_vec_ok) {
+#pragma unroll
+            for (int d = 0; d < kMaxDst; ++d) {
+                if (d >= p.ndst) break;
+                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(p.C[d]) + elem_off);
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            }
+        } else {
+            for (int d = 0; d < p.ndst; ++d) {
+                uint16_t *dst = reinterpret_cast<uint16_t *>(p.C[d]) + elem_off;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < ncols_valid) dst[j] = (uint16_t)((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xFFFFu));
+            }
+        }
+    }
+}
+
+template <int BN, int DT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p)
+{
+    using Cfg = TileCfg<BN, DT>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[Cfg::kStages];
+    __shared__ __align__(8) uint64_t bar_empty[Cfg::kStages];
+    __shared__ __align__(8) uint64_t bar_tmem_full[2];
+    __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+    __shared__ uint32_t tmem_base_holder;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u; // swizzle atoms need 1024-byte alignment
+    const int total_tiles = p.batch * p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < Cfg::kStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bar_tmem_full[a]), 1);
+            mbar_init(smem_u32(&bar_tmem_empty[a]), 4); // one arrival per epilogue warp
+        }
+        fence_mbar_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(&tmem_base_holder), Cfg::kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_holder;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const TileCoord tc = decode_tile(p, tile);
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = smem_u32(&bar_full[stage]);
+                    const uint32_t sbase = smem_base + stage * Cfg::kStageBytes;
+                    mbar_expect_tx(full, Cfg::kStageBytes);
+                    const int k0 = kb * Cfg::kBKE;
+#pragma unroll
+                    for (int pl = 0; pl < Cfg::kPlanes; ++pl) {
+                        const int z = Cfg::kTf32 ? pl : tc.b;
+                        tma_load_3d(sbase + pl * Cfg::kABytes, &tmA, k0, tc.m * BM, z, full);
+                        const uint32_t bbase = sbase + Cfg::kPlanes * Cfg::kABytes + pl * Cfg::kBBytes;
+                        if constexpr (Cfg::kBMnMajor) {
+#pragma unroll
+                            for (int c = 0; c < Cfg::kChunks; ++c)
+                                tma_load_3d(bbase + c * Cfg::kChunkBytes, &tmB, tc.n * BN + c * Cfg::kChunkN, k0, z, full);
+                        } else {
+                            tma_load_3d(bbase, &tmB, k0, tc.n * BN, z, full);
+                        }
+                    }
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(Cfg::kTf32 ? 2u : (DT == BTM_BF16 ? 1u : 0u), false, Cfg::kBMnMajor, BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag, p.status, WAIT_MMA_TMEM_EMPTY)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.status, WAIT_MMA_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sbase = smem_base + stage * Cfg::kStageBytes;
+                    const uint32_t a0 = sbase, b0 = sbase + Cfg::kPlanes * Cfg::kABytes;
+#pragma unroll
+                    for (int ks = 0; ks < Cfg::kKSteps; ++ks) {
+                        // A: K-major, 8-row groups 1024 B apart; a k-step moves 32 B inside the swizzle span.
+                        // B: MN-major, n-chunks kChunkBytes apart (leading offset), 8-k-row groups 1024 B
+                        // apart (stride offset); a k-step moves kUmmaKRows rows of 128 B.
+                        const uint64_t a_hi = make_smem_desc_sw128(a0 + ks * UMMA_K_BYTES, 16, 1024);
+                        const uint64_t b_hi = Cfg::kBMnMajor
+                                                  ? make_smem_desc_sw128(b0 + ks * Cfg::kUmmaKRows * SLICE_BYTES, Cfg::kChunkBytes, 1024)
+                                                  : make_smem_desc_sw128(b0 + ks * UMMA_K_BYTES, 16, 1024);
+                        const uint32_t first = (kb | ks) != 0;
+                        if constexpr (Cfg::kTf32) {
+                            const uint64_t a_lo = make_smem_desc_sw128(a0 + Cfg::kABytes + ks * UMMA_K_BYTES, 16, 1024);
+                            const uint64_t b_lo = make_smem_desc_sw128(b0 + Cfg::kBBytes + ks * UMMA_K_BYTES, 16, 1024);
+                            umma<1, true>(d_tmem, a_lo, b_hi, idesc, first);
+                            umma<1, true>(d_tmem, a_hi, b_lo, idesc, 1u);
+                            umma<1, true>(d_tmem, a_hi, b_hi, idesc, 1u);
+                        } else {
+                            umma<1, false>(d_tmem, a_hi, b_hi, idesc, first);
+                        }
+                    }
+                    umma_commit(smem_u32(&bar_empty[stage])); // stage reusable once these MMAs have read it
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(smem_u32(&bar_tmem_full[acc]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quad = warp & 3; // tensor-memory lane quadrant this warp may read
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            const TileCoord tc = decode_tile(p, tile);
+            const int acc = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            // The verdict must be warp-uniform: tcgen05.ld below needs the whole warp.
+            const bool ready = mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+            if (!__all_sync(0xffffffffu, ready)) break;
+            tc_fence_after();
+            const int row = tc.m * BM + quad * 32 + lane;
+            const long long row_off = (long long)tc.b * p.strideC + (long long)row * p.ldc + p.col0;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+                tmem_ld_wait();
+                const int col = tc.n * BN + c * 32;
+                const int valid = min(32, p.N - col);
+                if (row < p.M && valid > 0) store_row_chunk<DT>(p, v, row_off + col, valid);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        // A wait ran out somewhere. Copies already issued by the producer finish on their own
+        // within microseconds; give them a bounded grace period before shared memory is released.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// 3xTF32 operand preparation: hi = x with the low 13 mantissa bits cleared (what the tensor
+// core reads of an fp32 word), lo = x - hi (exact in fp32). Written as two dense planes.
+__global__ void split_tf32_kernel(const float *__restrict__ src, long long ld, int rows, int cols,
+                                  float *__restrict__ hi, float *__restrict__ lo, long long ld_dst)
+{
+    const long long total = (long long)rows * ld_dst;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / ld_dst;
+        const int c = (int)(i - r * ld_dst);
+        float x = (c < cols) ? src[r * ld + c] : 0.0f;
+        const float h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+        hi[i] = h;
+        lo[i] = x - h;
+    }
+}
+
+// Same split for B, written transposed: src is [rows=K, cols=N] row-major, the planes are
+// [N, ld_dst] (K contiguous) so that the tensor cores read B K-major like A.
+__global__ void split_tf32_transpose_kernel(const float *__restrict__ src, long long ld, int rows, int cols,
+                                            float *__restrict__ hi, float *__restrict__ lo, long long ld_dst)
+{
+    __shared__ float tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int r = r0 + i, c = c0 + threadIdx.x;
+        tile[i][threadIdx.x] = (r < rows && c < cols) ? src[(long long)r * ld + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int c = c0 + i, r = r0 + threadIdx.x; // output row = source column
+        if (c < cols && r < ld_dst) {
+            const float x = tile[threadIdx.x][i];
+            const float h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+            hi[(long long)c * ld_dst + r] = h;
+            lo[(long long)c * ld_dst + r] = x - h;
+        }
+    }
+}
+
+int launch_split_tf32_transpose(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
+                                float *dst_lo, long long ld_dst)
+{
+    if (rows == 0 || cols == 0) return BTM_OK;
+    dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((ld_dst + 31) / 32));
+    if (grid.y > 65535) return set_error(BTM_ERR_UNSUPPORTED, "fp32 matmul: K too large for the split pass");
+    split_tf32_transpose_kernel<<<grid, dim3(32, 8), 0, st>>>(src, ld, rows, cols, dst_hi, dst_lo, ld_dst);
+    return check_cuda(cudaGetLastError(), "split_tf32_transpose launch");
+}
+
+int launch_split_tf32(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
+                      float *dst_lo, long long ld_dst)
+{
+    const long long total = (long long)rows * ld_dst;
+    if (total == 0) return BTM_OK;
+    const int block = 256;
+    const long long want = (total + block - 1) / block;
+    const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+    split_tf32_kernel<<<grid, block, 0, st>>>(src, ld, rows, cols, dst_hi, dst_lo, ld_dst);
+    return check_cuda(cudaGetLastError(), "split_tf32 launch");
+}
+
+template <int BN, int DT>
+static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, GemmParams p)
+{
+    using Cfg = TileCfg<BN, DT>;
+    p.tiles_m = (p.M + BM - 1) / BM;
+    p.tiles_n = (p.N + BN - 1) / BN;
+    p.num_kb = (p.K + Cfg::kBKE - 1) / Cfg::kBKE;
+    if (p.group_m <= 0) p.group_m = 8;
+    const long long total = (long long)p.batch * p.tiles_m * p.tiles_n;
+    if (total <= 0) return BTM_OK;
+    if (total > 0x7FFFFFFFLL) return set_error(BTM_ERR_UNSUPPORTED, "too many output tiles (%lld)", total);
+    const int grid = (int)(total < sm_count ? total : sm_count);
+    gemm_tc_kernel<BN, DT><<<grid, NUM_THREADS, Cfg::kSmemBytes, st>>>(tmA, tmB, p);
+    return check_cuda(cudaGetLastError(), "gemm_tc launch");
+}
+
+template <int BN, int DT>
+static cudaError_t raise_smem()
+{
+    return cudaFuncSetAttribute(gemm_tc_kernel<BN, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                TileCfg<BN, DT>::kSmemBytes);
+}
+
+int configure_gemm_tc_kernels()
+{
+    cudaError_t e = cudaSuccess;
+    if (e == cudaSuccess) e = raise_smem<256, BTM_F16>();
+    if (e == cudaSuccess) e = raise_smem<256, BTM_BF16>();
+    if (e == cudaSuccess) e = raise_smem<128, BTM_F16>();
+    if (e == cudaSuccess) e = raise_smem<128, BTM_BF16>();
+    if (e == cudaSuccess) e = raise_smem<128, BTM_F32>();
+    if (e == cudaSuccess) e = raise_smem<64, BTM_F32>();
+    return check_cuda(e, "cudaFuncSetAttribute(gemm_tc)");
+}
+
+int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB,
+                   const GemmParams &p, int force_bn)
+{
+    // Tile width: 256 columns unless the output is so small that narrower tiles are needed to
+    // give every SM work.
+    if (dtype == BTM_F32) {
+        int bn = force_bn ? force_bn : 128;
+        if (!force_bn) {
+            const long long t128 = (long long)p.batch * ((p.M + BM - 1) / BM) * ((p.N + 127) / 128);
+            if (t128 < sm_count) bn = 64;
+        }
+        if (bn == 64) return launch_one<64, BTM_F32>(st, sm_count, tmA, tmB, p);
+        return launch_one<128, BTM_F32>(st, sm_count, tmA, tmB, p);
+    }
+    int bn = force_bn ? force_bn : 256;
+    if (!force_bn) {
+        const long long t256 = (long long)p.batch * ((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+        if (t256 < sm_count) bn = 128;
+    }
+    if (dtype == BTM_F16) {
+        if (bn == 128) return launch_one<128, BTM_F16>(st, sm_count, tmA, tmB, p);
+        return launch_one<256, BTM_F16>(st, sm_count, tmA, tmB, p);
+    }
+    if (bn == 128) return launch_one<128, BTM_BF16>(st, sm_count, tmA, tmB, p);
+    return launch_one<256, BTM_BF16>(st, sm_count, tmA, tmB, p);
+}
+
+} // namespace btm

@@ -1,0 +1,150 @@
+"""Host-side mirror of the reference's GPU operator boundary for the matmul path.
+
+The reference declares its GPU operators as free functions `detail::*_gpu(Tensor&, ...)`
+(Tensor/TensorOps.h:15-65) that check the device, then enqueue work and leave the result in a
+pre-allocated tensor. The functions here have the names and argument meaning a
+`matmul_gpu` / `bmm_gpu` / `matmul_int4_gpu` family added beside them would have; torch
+tensors stand in for BeanTensor's Tensor (torch is used for device memory and streams only —
+every product is computed by libbtm.so).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from .errors import GPUTaskOnCPUBuild, raise_for_status
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
+
+
+def _require_gpu(*tensors: torch.Tensor) -> int:
+    if not torch.cuda.is_available():
+        raise GPUTaskOnCPUBuild("GPU task cannot be run on CPU build")  # TensorOps.hpp:5-30
+    dev = None
+    for t in tensors:
+        if t.device.type != "cuda":
+            raise ValueError("Tensor is not on the GPU")  # guard of Tensor/TensorOps.cu:89-93
+        if dev is None:
+            dev = t.device.index
+        elif t.device.index != dev:
+            raise ValueError("Tensors live on different GPUs")
+    return int(dev)
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _rowmajor(t: torch.Tensor, name: str) -> None:
+    if t.stride(-1) != 1 and t.size(-1) > 1:
+        raise ValueError(f"{name} must be row-major (last stride 1)")  # Tensor/Tensor.cpp:157-162
+
+
+def init(device: int = 0) -> None:
+    raise_for_status(_lib.lib().btm_init(device))
+
+
+def check_device_status(device: int = 0) -> None:
+    raise_for_status(_lib.lib().btm_check_device_status(device, _stream()))
+
+
+def matmul_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] . b[K,N]; fp16/bf16 (fp32 accumulate) or fp32 (3xTF32)."""
+    dev = _require_gpu(a, b, out)
+    if a.dim() != 2 or b.dim() != 2 or out.dim() != 2:
+        raise ValueError("matmul_gpu takes 2-D tensors")
+    if a.dtype != b.dtype or a.dtype != out.dtype:
+        raise ValueError("matmul_gpu: dtypes differ")
+    if a.dtype not in _DT:
+        from .errors import NotImplementedOp
+        raise NotImplementedOp(f"matmul_gpu: dtype {a.dtype} is not supported")
+    M, K = a.shape
+    K2, N = b.shape
+    if K != K2 or out.shape != (M, N):
+        raise ValueError(f"matmul_gpu: shape mismatch {tuple(a.shape)} x {tuple(b.shape)} -> {tuple(out.shape)}")
+    for t, n in ((a, "a"), (b, "b"), (out, "out")):
+        _rowmajor(t, n)
+    lda = a.stride(0) if M > 1 else max(K, 1)
+    ldb = b.stride(0) if K > 1 else max(N, 1)
+    ldc = out.stride(0) if M > 1 else max(N, 1)
+    rc = _lib.lib().btm_gemm(dev, _stream(), _DT[a.dtype], M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
+                             out.data_ptr(), ldc)
+    raise_for_status(rc)
+
+
+def bmm_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b] = a[b] . b[b] for dense row-major 3-D tensors (fp16/bf16)."""
+    dev = _require_gpu(a, b, out)
+    if a.dim() != 3 or b.dim() != 3 or out.dim() != 3:
+        raise ValueError("bmm_gpu takes 3-D tensors")
+    if a.dtype != b.dtype or a.dtype != out.dtype:
+        raise ValueError("bmm_gpu: dtypes differ")
+    if a.dtype not in (torch.float16, torch.bfloat16):
+        from .errors import NotImplementedOp
+        raise NotImplementedOp(f"bmm_gpu: dtype {a.dtype} is not supported")
+    B, M, K = a.shape
+    B2, K2, N = b.shape
+    if B != B2 or K != K2 or out.shape != (B, M, N):
+        raise ValueError("bmm_gpu: shape mismatch")
+    for t in (a, b, out):
+        if not t[0].is_contiguous() if B > 0 else False:
+            raise ValueError("bmm_gpu: each matrix must be dense row-major")
+    sa = a.stride(0) if B > 1 else M * K
+    sb = b.stride(0) if B > 1 else K * N
+    sc = out.stride(0) if B > 1 else M * N
+    rc = _lib.lib().btm_bmm(dev, _stream(), _DT[a.dtype], B, M, N, K, a.data_ptr(), sa, b.data_ptr(), sb,
+                            out.data_ptr(), sc)
+    raise_for_status(rc)
+
+
+def matmul_int4_gpu(act: torch.Tensor, w_packed: torch.Tensor, scales: torch.Tensor, out: torch.Tensor,
+                    group: int = 128) -> None:
+    """out[M,N] (fp16) = act[M,K] (fp16) . dequant(w_packed[N,K/2], scales[N,K/group])^T."""
+    dev = _require_gpu(act, w_packed, scales, out)
+    if act.dtype != torch.float16 or scales.dtype != torch.float16 or out.dtype != torch.float16:
+        raise ValueError("matmul_int4_gpu: activations, scales and output are Float16")
+    if w_packed.dtype != torch.uint8:
+        raise ValueError("matmul_int4_gpu: packed weights are bytes (two nibbles each)")
+    M, K = act.shape
+    N = w_packed.shape[0]
+    if w_packed.shape != (N, K // 2) or scales.shape != (N, K // group if group else 0) or out.shape != (M, N):
+        raise ValueError("matmul_int4_gpu: shape mismatch")
+    for t in (act, w_packed, scales, out):
+        if not t.is_contiguous():
+            raise ValueError("matmul_int4_gpu: tensors must be contiguous")
+    rc = _lib.lib().btm_int4_matmul(dev, _stream(), M, N, K, group, act.data_ptr(), w_packed.data_ptr(),
+                                    scales.data_ptr(), out.data_ptr())
+    raise_for_status(rc)
+
+
+def dequant_int4_gpu(w_packed: torch.Tensor, scales: torch.Tensor, out: torch.Tensor, group: int = 128) -> None:
+    dev = _require_gpu(w_packed, scales, out)
+    N, K2 = w_packed.shape
+    K = K2 * 2
+    if out.shape != (N, K) or out.dtype != torch.float16 or scales.dtype != torch.float16:
+        raise ValueError("dequant_int4_gpu: shape or dtype mismatch")
+    rc = _lib.lib().btm_int4_dequant(dev, _stream(), N, K, group, w_packed.data_ptr(), scales.data_ptr(), out.data_ptr())
+    raise_for_status(rc)
+
+
+def unpack_int4_gpu(w_packed: torch.Tensor, out: torch.Tensor) -> None:
+    dev = _require_gpu(w_packed, out)
+    N, K2 = w_packed.shape
+    if out.shape != (N, K2 * 2) or out.dtype != torch.int8:
+        raise ValueError("unpack_int4_gpu: shape or dtype mismatch")
+    rc = _lib.lib().btm_int4_unpack(dev, _stream(), N, K2 * 2, w_packed.data_ptr(), out.data_ptr())
+    raise_for_status(rc)
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """User-level wrapper in the style of the reference's Ops::add sketch
+    (Ops/Elementwise/Add/Add.h:28-73): checks, allocates the result, dispatches by rank."""
+    if a.dim() == 3:
+        out = torch.empty((a.shape[0], a.shape[1], b.shape[2]), dtype=a.dtype, device=a.device)
+        bmm_gpu(a, b, out)
+        return out
+    out = torch.empty((a.shape[0], b.shape[1]), dtype=a.dtype, device=a.device)
+    matmul_gpu(a, b, out)
+    return out

@@ -1,0 +1,174 @@
+/*
+ * btm.h — C ABI of libbtm.so, the sm_100a matmul subsystem that sits behind BeanTensor's
+ * GPU operator boundary (namespace BeanTensor::Tensors::detail, Tensor/TensorOps.h:15-65).
+ *
+ * The reference declares its GPU operators as free functions taking Tensor& and running
+ * on a thread-pool worker (Tensor/TensorOps.cu:89-208). It has no matmul of its own
+ * (Ops/Algebra/MatMul/MatMul.h:1-8 is an empty include guard), so each entry point below
+ * names the reference interface it extends or stands in for. A BeanTensor maintainer
+ * binds these from a `detail::matmul_gpu(const Tensor&, const Tensor&, Tensor&)` style
+ * function; beantensor_b200/host/MatMulOps.h is that binding.
+ *
+ * Conventions shared by every call
+ *   - plain pointers and sizes only; all matrices are row-major with leading dimensions
+ *     in ELEMENTS (Tensor/Tensor.cpp:157-162);
+ *   - `dtype` is the reference's DType ordinal (Tensor/Dtypes.h:57-70);
+ *   - `device` is the CUDA ordinal (Tensor::gpu_id, Tensor/Tensor.h:191); the call makes
+ *     it current on the calling thread itself, because the reference's pool threads set
+ *     it inconsistently (Tensor/TensorOps.cu:232-259 does, :89-208 does not);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the null stream, which is what
+ *     the reference always uses, Tensor/Tensor.h:187); work is enqueued, not awaited;
+ *   - the caller owns every buffer; outputs are pre-allocated (ops never reallocate
+ *     Tensor::data, cf. Tensor/TensorOps.cu:89-208);
+ *   - the return value is a btm_status; a C ABI cannot throw, so the C++ binding maps the
+ *     status back to the reference's exception types (Errors/Logic.h:13-38);
+ *   - calls are re-entrant and may come from any thread (Helper/Threads/CPUThreading.h:37-56).
+ * There is no CPU fallback: without a usable sm_100 device every compute call fails with
+ * BTM_ERR_CUDA or BTM_ERR_UNSUPPORTED.
+ */
+#ifndef BTM_H
+#define BTM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes. Mapping in the C++ binding: INVALID -> std::invalid_argument
+ * (Tensor/TensorOps.cu:241,269), UNSUPPORTED -> ErrorHandling::NotImplemented
+ * (Errors/Logic.h:13-17), OOM -> ErrorHandling::OutOfMemory (Errors/Logic.h:22-25),
+ * CUDA/NCCL/TIMEOUT -> std::runtime_error("CUDA Error: ...") (Errors/Logic.h:50-59). */
+typedef enum btm_status {
+    BTM_OK = 0,
+    BTM_ERR_INVALID = 1,
+    BTM_ERR_UNSUPPORTED = 2,
+    BTM_ERR_OOM = 3,
+    BTM_ERR_CUDA = 4,
+    BTM_ERR_NCCL = 5,
+    BTM_ERR_TIMEOUT = 6
+} btm_status;
+
+/* DType ordinals: identical to enum class DType, Tensor/Dtypes.h:57-70. INT4X2 is
+ * appended (the reference has no sub-byte type) so ordinals 0..11 keep their meaning:
+ * one byte holds two signed 4-bit values, even k in bits 0-3, odd k in bits 4-7. */
+typedef enum btm_dtype {
+    BTM_BF16 = 0,
+    BTM_F16 = 1,
+    BTM_F32 = 2,
+    BTM_F64 = 3,
+    BTM_I64 = 4,
+    BTM_I32 = 5,
+    BTM_I16 = 6,
+    BTM_I8 = 7,
+    BTM_U64 = 8,
+    BTM_U32 = 9,
+    BTM_U16 = 10,
+    BTM_U8 = 11,
+    BTM_INT4X2 = 12
+} btm_dtype;
+
+/* POD mirror of the fields of class Tensor that the path reads (Tensor/Tensor.h:173-201):
+ * shape and strides in elements, at most 8 dims, offset in elements. */
+typedef struct btm_tensor_view {
+    void *data;
+    int32_t dtype;  /* btm_dtype */
+    int32_t device; /* 0 = CPU, 1 = GPU (enum class Device, Tensor/Tensor.h:34-37) */
+    int32_t gpu_id;
+    int32_t ndim;
+    uint64_t shape[8];
+    uint64_t strides[8];
+    uint64_t offset;
+} btm_tensor_view;
+
+/* Element size in bytes of a dtype ordinal (dtype_size, Tensor/Dtypes.h:75-92);
+ * BTM_INT4X2 reports 1 (one byte = two elements); unknown ordinals report 0. */
+size_t btm_dtype_size(int dtype);
+
+/* Library version, major*10000 + minor*100 + patch. */
+int btm_version(void);
+
+/* Text of the last error raised on the calling thread (never NULL). Plays the role of
+ * the what() string of the exceptions the reference throws (Errors/Logic.h:13-59). */
+const char *btm_last_error_string(void);
+
+/* Prepare `device`: checks that it is an sm_100 part, creates the per-device state
+ * (status word, kernel attributes). Every compute call does this lazily; call it up front
+ * to keep the first timed call clean. Stands where the reference's workers do their
+ * device checks (Tensor/TensorOps.cu:236-247). */
+int btm_init(int device);
+
+/* Reads and clears the device-side status word that kernels set when one of their
+ * bounded waits ran out. Synchronises `stream`. Returns BTM_OK or BTM_ERR_TIMEOUT. */
+int btm_check_device_status(int device, void *stream);
+
+/* Dense matmul C[M,N] = A[M,K] . B[K,N], the op that Ops/Algebra/MatMul/MatMul.h:1-8
+ * leaves empty; to be called from a detail::matmul_gpu() declared beside the functions of
+ * Tensor/TensorOps.h:18-63.
+ *   dtype BTM_F16 / BTM_BF16: fp32 accumulation on the tensor cores, output rounded to
+ *   nearest even into the same 16-bit type (as Tensor/TensorOps.cu:72 rounds).
+ *   dtype BTM_F32: three-term TF32 split (hi.hi + hi.lo + lo.hi) with fp32 accumulation;
+ *   needs (M + N) * roundup(K,4) * 8 bytes of scratch that the library keeps per device and grows
+ *   with cudaMalloc on demand (first call of a larger shape allocates).
+ * lda >= K, ldb >= N, ldc >= N, in elements. Any M, N, K >= 0; shapes or pointers that
+ * the tensor-core path cannot address (row pitch or base not 16-byte aligned) run on a
+ * general CUDA-core kernel with the same arithmetic contract. */
+int btm_gemm(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B,
+             int64_t ldb, void *C, int64_t ldc);
+
+/* Same product for BTM_F32 with caller-owned scratch instead of the library's:
+ * `workspace` is device memory of at least btm_gemm_f32_workspace_bytes(M,N,K) bytes,
+ * 256-byte aligned. Nothing is allocated. */
+size_t btm_gemm_f32_workspace_bytes(int M, int N, int K);
+int btm_gemm_f32_ws(int device, void *stream, int M, int N, int K, const void *A, int64_t lda, const void *B,
+                    int64_t ldb, void *C, int64_t ldc, void *workspace, size_t workspace_bytes);
+
+/* Batched matmul: `batch` independent products C[b] = A[b] . B[b] with element strides
+ * between consecutive matrices; each matrix is row-major and dense (lda=K, ldb=N, ldc=N).
+ * The reference has no such op (not even a stub); it extends Ops/Algebra/MatMul the same
+ * way. dtype BTM_F16 or BTM_BF16. One persistent launch walks all (batch, tile) pairs. */
+int btm_bmm(int device, void *stream, int dtype, int batch, int M, int N, int K, const void *A, int64_t strideA,
+            const void *B, int64_t strideB, void *C, int64_t strideC);
+
+/* int4 weight-only matmul: out[M,N] (fp16) = act[M,K] (fp16) . dequant(W)[N,K]^T with
+ * W packed two nibbles per byte along K ([N, K/2] bytes) and one fp16 scale per `group`
+ * consecutive k ([N, K/group]). The dtype is this build's addition to Tensor/Dtypes.h:57-70.
+ * Arithmetic: fp32 accumulation of act*w inside a group, times the scale, summed over
+ * groups, rounded to nearest even. K % group == 0, group % 32 == 0, K % 32 == 0. */
+int btm_int4_matmul(int device, void *stream, int M, int N, int K, int group, const void *act_f16,
+                    const void *w_packed, const void *scales_f16, void *out_f16);
+
+/* Bit-exact dequantisation of the packed weights to fp16 [N,K]:
+ * out[n,k] = f16_rne(float(W[n,k]) * float(S[n,k/group])). Plays the role of a
+ * convert_gpu() case (Tensor/TensorOps.cu:315-365) for the appended dtype. */
+int btm_int4_dequant(int device, void *stream, int N, int K, int group, const void *w_packed,
+                     const void *scales_f16, void *out_f16);
+
+/* Unpack only: int8 out[n,k] = W[n,k] in [-8,7]. */
+int btm_int4_unpack(int device, void *stream, int N, int K, const void *w_packed, void *out_i8);
+
+/* N-sharded matmul with the all-gather fused into the epilogue: this rank holds all of A
+ * and the column block B[:, rank*Nloc:(rank+1)*Nloc]; it computes C[:, that block] and
+ * stores every finished tile into the full row-major C of EVERY rank through peer-mapped
+ * pointers (`C_ranks[r]` is rank r's C base, valid on this device; ldc = nranks*Nloc or
+ * more). Takes the place of the reference's only multi-GPU primitive, the whole-tensor
+ * cudaMemcpyPeer of move_gpu_to_gpu (Tensor/TensorOps.cu:282-313). The caller provides
+ * the cross-rank barrier before C is read. dtype BTM_F16 or BTM_BF16. */
+int btm_gemm_nshard(int device, void *stream, int dtype, int M, int Nloc, int K, const void *A, int64_t lda,
+                    const void *B_local, int64_t ldb, void *const *C_ranks, int64_t ldc, int rank, int nranks);
+
+/* CUDA IPC helpers so that one-process-per-GPU callers can build `C_ranks`:
+ * btm_ipc_alloc allocates `bytes` of device memory and writes a 64-byte handle;
+ * btm_ipc_open maps a peer's handle on `device`; btm_ipc_close / btm_ipc_free undo them.
+ * (The reference is single-process and reaches peers with cudaDeviceEnablePeerAccess,
+ * Tensor/TensorOps.cu:300-301.) */
+int btm_ipc_alloc(int device, size_t bytes, void **ptr, unsigned char handle[64]);
+int btm_ipc_open(int device, const unsigned char handle[64], void **ptr);
+int btm_ipc_close(int device, void *ptr);
+int btm_ipc_free(int device, void *ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BTM_H */

@@ -1,0 +1,139 @@
+"""Parity of the dense matmul (btm_gemm through the operator mirror) with the CPU oracle."""
+import numpy as np
+import pytest
+
+from beantensor_b200 import _lib
+from tests.helpers import TOL, gemm_inputs, to_gpu, to_host_bits, torch_dtype
+
+pytestmark = pytest.mark.gpu
+
+EDGE = [1, 7, 8, 64, 65, 127, 128, 129, 257]
+
+
+def run_case(btm, oracle, dtype, M, N, K, seed=11, dist="normal"):
+    import torch
+    A, B = gemm_inputs(dtype, M, N, K, seed, dist)
+    a, b = to_gpu(A, dtype), to_gpu(B, dtype)
+    out = torch.full((M, N), float("nan"), dtype=torch_dtype(dtype), device="cuda")
+    btm.matmul_gpu(a, b, out)
+    btm.check_device_status(0)
+    got = to_host_bits(out, dtype)
+    ref = oracle.gemm(dtype, A, B)
+    err = oracle.rel_frobenius(got, dtype, ref)
+    return err, got, ref
+
+
+@pytest.mark.parametrize("dtype", [_lib.F16, _lib.BF16, _lib.F32])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 512), (384, 640, 1024), (1000, 1000, 992), (130, 72, 40)])
+def test_aligned_shapes(btm, oracle, dtype, shape):
+    err, _, _ = run_case(btm, oracle, dtype, *shape)
+    assert err <= TOL[dtype], (shape, err)
+
+
+@pytest.mark.parametrize("dtype", [_lib.F16, _lib.BF16, _lib.F32])
+def test_edge_shapes(btm, oracle, dtype):
+    # Every combination on the diagonal plus mixed triples: covers the tensor-core path with
+    # ragged tiles, and the general kernel where the row pitch is not a multiple of 16 bytes.
+    triples = [(m, m, m) for m in EDGE] + [(1, 257, 64), (257, 1, 128), (129, 65, 7), (8, 264, 72), (64, 8, 1)]
+    for (M, N, K) in triples:
+        err, _, _ = run_case(btm, oracle, dtype, M, N, K, seed=M * 3 + N * 5 + K)
+        assert err <= TOL[dtype], ((M, N, K), err)
+
+
+def test_reference_workload_fp32_1024(btm, oracle):
+    # fp32, M=N=K=1024, U[-1,1] (the reference's CPU-runnable workload shape).
+    err, _, _ = run_case(btm, oracle, _lib.F32, 1024, 1024, 1024, seed=0, dist="uniform")
+    assert err <= 1e-5, err
+
+
+def test_reference_workload_fp32_with_reference_rng(btm, oracle):
+    # Same workload with A and B drawn by the restated reference generator (Tensor::random(-1,1,0)).
+    import torch
+    A = oracle.ref_random_f32((512, 512), 0, -1.0, 1.0, 8)
+    B = oracle.ref_random_f32((512, 512), 1, -1.0, 1.0, 8)
+    out = torch.empty((512, 512), dtype=torch.float32, device="cuda")
+    btm.matmul_gpu(torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), out)
+    assert oracle.rel_frobenius(out.cpu().numpy(), _lib.F32, oracle.gemm(_lib.F32, A, B)) <= 1e-5
+
+
+def test_zero_k_and_empty(btm, oracle):
+    import torch
+    a = torch.empty((5, 0), dtype=torch.float16, device="cuda")
+    b = torch.empty((0, 3), dtype=torch.float16, device="cuda")
+    out = torch.full((5, 3), 7.0, dtype=torch.float16, device="cuda")
+    btm.matmul_gpu(a, b, out)
+    assert torch.count_nonzero(out).item() == 0
+    out0 = torch.empty((0, 3), dtype=torch.float16, device="cuda")
+    btm.matmul_gpu(torch.empty((0, 4), dtype=torch.float16, device="cuda"), torch.empty((4, 3), dtype=torch.float16, device="cuda"), out0)
+
+
+def test_strided_operands_and_untouched_padding(btm, oracle):
+    # lda/ldb/ldc larger than the logical width; columns beyond N must stay untouched.
+    import torch
+    dtype = _lib.F16
+    M, N, K = 200, 136, 96
+    A, B = gemm_inputs(dtype, M, N, K, 3)
+    a_full = torch.zeros((M, K + 8), dtype=torch.float16, device="cuda")
+    b_full = torch.zeros((K, N + 16), dtype=torch.float16, device="cuda")
+    c_full = torch.full((M, N + 24), -5.0, dtype=torch.float16, device="cuda")
+    a_full[:, :K] = to_gpu(A, dtype)
+    b_full[:, :N] = to_gpu(B, dtype)
+    btm.matmul_gpu(a_full[:, :K], b_full[:, :N], c_full[:, :N])
+    got = to_host_bits(c_full[:, :N].contiguous(), dtype)
+    assert oracle.rel_frobenius(got, dtype, oracle.gemm(dtype, A, B)) <= TOL[dtype]
+    assert torch.all(c_full[:, N:] == -5.0)
+
+
+def test_errors_follow_reference_convention(btm):
+    import torch
+    from beantensor_b200.errors import NotImplementedOp
+    a = torch.zeros((4, 4), dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        btm.matmul_gpu(a, torch.zeros((5, 4), dtype=torch.float16, device="cuda"), a.clone())
+    with pytest.raises(NotImplementedOp):
+        i = torch.zeros((4, 4), dtype=torch.int32, device="cuda")
+        btm.matmul_gpu(i, i, i.clone())
+    with pytest.raises(ValueError):
+        btm.matmul_gpu(a.cpu(), a, a.clone())
+
+
+@pytest.mark.parametrize("dtype", [_lib.F16, _lib.BF16])
+def test_full_size_properties(btm, oracle, dtype):
+    # 4096^3 is beyond what the CPU oracle finishes in seconds, so check size-independent
+    # properties: (1) sampled rows against the oracle, (2) linearity in A, (3) column-sum identity
+    # 1^T (A B) = (1^T A) B evaluated in fp64.
+    import torch
+    M = N = K = 4096
+    A, B = gemm_inputs(dtype, M, N, K, 1)
+    a, b = to_gpu(A, dtype), to_gpu(B, dtype)
+    out = torch.empty((M, N), dtype=torch_dtype(dtype), device="cuda")
+    btm.matmul_gpu(a, b, out)
+    btm.check_device_status(0)
+    rows = np.array([0, 1, 127, 128, 2047, 2048, 3000, 4095])
+    ref_rows = oracle.gemm(dtype, np.ascontiguousarray(A[rows]), B)
+    got_rows = to_host_bits(out[torch.from_numpy(rows).cuda()], dtype)
+    assert oracle.rel_frobenius(got_rows, dtype, ref_rows) <= TOL[dtype]
+    # checksum of checksums
+    colsum_gpu = out.double().sum(dim=0).cpu().numpy()
+    colsum_ref = (oracle.widen(A, dtype).sum(axis=0)[None, :] @ oracle.widen(B, dtype)).ravel()
+    assert np.linalg.norm(colsum_gpu - colsum_ref) / np.linalg.norm(colsum_ref) <= TOL[dtype]
+    # linearity: (2A) B == 2 (A B) bit for bit wherever the result is a normal number (scaling by 2
+    # is exact in binary floating point; in the subnormal range of the output type the rounding
+    # quantum is fixed, so there the two may differ by one quantum).
+    out2 = torch.empty_like(out)
+    btm.matmul_gpu(a * 2, b, out2)
+    tiny = 2.0 ** -14 if dtype == _lib.F16 else 2.0 ** -126
+    normal = out.float().abs() >= tiny
+    assert torch.equal(out2[normal], (out * 2)[normal])
+    quantum = 2.0 ** -24 if dtype == _lib.F16 else 2.0 ** -133
+    assert (out2.float() - out.float() * 2).abs().max().item() <= quantum
+
+
+def test_repeatable(btm):
+    import torch
+    a = torch.randn((512, 512), device="cuda").half()
+    b = torch.randn((512, 512), device="cuda").half()
+    o1, o2 = torch.empty_like(a), torch.empty_like(a)
+    btm.matmul_gpu(a, b, o1)
+    btm.matmul_gpu(a, b, o2)
+    assert torch.equal(o1, o2)

@@ -1,0 +1,98 @@
+"""int4 weight-only path: bit-exact unpack and dequant, matmul within 2e-3 of the oracle."""
+import os
+
+import numpy as np
+import pytest
+
+from beantensor_b200 import synth
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def make(M, N, K, group, seed):
+    w = synth.int4((N, K), seed)
+    packed = synth.pack_int4(w)
+    s = synth.uniform((N, K // group), 0.005, 0.02, seed, 1).astype(np.float16)
+    act = synth.normal((M, K), 1.0, seed, 2).astype(np.float16)
+    return w, packed, s, act
+
+
+def gpu_matmul(btm, act, packed, s, group):
+    import torch
+    out = torch.full((act.shape[0], packed.shape[0]), float("nan"), dtype=torch.float16, device="cuda")
+    btm.matmul_int4_gpu(torch.from_numpy(act).cuda(), torch.from_numpy(packed).cuda(), torch.from_numpy(s).cuda(), out, group)
+    return out.cpu().numpy()
+
+
+def test_golden_cases_bit_exact_dequant(btm, oracle):
+    import torch
+    g = np.load(os.path.join(GOLD, "int4_small.npz"))
+    for i in range(int(g["ncases"][0])):
+        M, N, K, group = (int(v) for v in g[f"case{i}_meta"])
+        packed = torch.from_numpy(g[f"case{i}_packed"]).cuda()
+        scales = torch.from_numpy(g[f"case{i}_scales"]).view(torch.float16).cuda()
+        deq = torch.empty((N, K), dtype=torch.float16, device="cuda")
+        btm.dequant_int4_gpu(packed, scales, deq, group)
+        assert np.array_equal(deq.cpu().view(torch.uint16).numpy(), g[f"case{i}_dequant"]), i
+        unp = torch.empty((N, K), dtype=torch.int8, device="cuda")
+        btm.unpack_int4_gpu(packed, unp)
+        assert np.array_equal(unp.cpu().numpy(), g[f"case{i}_w"]), i
+        act = g[f"case{i}_act"].view(np.float16)
+        out = gpu_matmul(btm, act, g[f"case{i}_packed"], g[f"case{i}_scales"].view(np.float16), group)
+        assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, g[f"case{i}_out"]) <= 2e-3, i
+
+
+@pytest.mark.parametrize("M", [1, 8, 64])
+def test_workload_shape(btm, oracle, M):
+    # N=11008, K=4096, group 128: the whole weight matrix, bit-exact dequant and 2e-3 output.
+    import torch
+    N, K, group = 11008, 4096, 128
+    w, packed, s, act = make(M, N, K, group, 2)
+    out = gpu_matmul(btm, act, packed, s, group)
+    ref = oracle.int4_matmul(act.view(np.uint16), packed, s.view(np.uint16), group)
+    assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, ref) <= 2e-3
+    if M == 1:
+        deq = torch.empty((N, K), dtype=torch.float16, device="cuda")
+        btm.dequant_int4_gpu(torch.from_numpy(packed).cuda(), torch.from_numpy(s).cuda(), deq, group)
+        assert np.array_equal(deq.cpu().view(torch.uint16).numpy(), oracle.int4_dequant(packed, s.view(np.uint16), group))
+        unp = torch.empty((N, K), dtype=torch.int8, device="cuda")
+        btm.unpack_int4_gpu(torch.from_numpy(packed).cuda(), unp)
+        assert np.array_equal(unp.cpu().numpy(), w)
+
+
+@pytest.mark.parametrize("case", [(1, 16, 128, 128), (2, 17, 256, 128), (5, 100, 1024, 256), (9, 33, 384, 128),
+                                  (3, 40, 96, 32), (1, 5, 64, 64), (8, 16, 8192, 128)])
+def test_ragged_and_general_shapes(btm, oracle, case):
+    # N not a multiple of 16, M crossing the 8-row block, groups other than 128 (general kernel).
+    M, N, K, group = case
+    w, packed, s, act = make(M, N, K, group, 17 + M + N)
+    out = gpu_matmul(btm, act, packed, s, group)
+    assert not np.isnan(out).any()
+    ref = oracle.int4_matmul(act.view(np.uint16), packed, s.view(np.uint16), group)
+    assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, ref) <= 2e-3
+
+
+def test_extreme_nibbles(btm, oracle):
+    # all -8, all 7, alternating: exercises the sign handling of the unpack
+    import torch
+    N, K, group = 32, 256, 128
+    for fill in (-8, 7, None):
+        w = np.full((N, K), fill if fill is not None else 0, dtype=np.int8)
+        if fill is None:
+            w[:, 0::2], w[:, 1::2] = -8, 7
+        packed = synth.pack_int4(w)
+        s = np.full((N, K // group), 0.0078125, dtype=np.float16)
+        act = np.ones((2, K), dtype=np.float16)
+        out = gpu_matmul(btm, act, packed, s, group)
+        want = w.astype(np.float64).sum(axis=1) * 0.0078125
+        assert np.allclose(out.astype(np.float64), np.broadcast_to(want, (2, N)), rtol=2e-3)
+
+
+def test_bad_arguments(btm):
+    import torch
+    act = torch.zeros((1, 100), dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        btm.matmul_int4_gpu(act, torch.zeros((16, 50), dtype=torch.uint8, device="cuda"),
+                            torch.zeros((16, 0), dtype=torch.float16, device="cuda"),
+                            torch.zeros((1, 16), dtype=torch.float16, device="cuda"), 128)
