@@ -1,0 +1,526 @@
+#!/usr/bin/env python
+"""Benchmark of the matmul path: fp16 GEMM TFLOP/s + int4 GEMV HBM GB/s against the B200 roofline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One JSON line on stdout (rank 0). A "step" is one product of the named workload:
+  N = 1   fp16 dense GEMM M=N=K=4096, fp32 accumulate (the workload the metric is quoted on);
+          the line also carries the other single-GPU workloads under "configs" (int4 GEMV/GEMM,
+          batched matmul, fp32 1024^3, bf16 16384^3) each with its own roofline figures.
+  N > 1   bf16 GEMM M=N=K=16384 with B split by N-columns over the ranks; every rank computes its
+          column block and stores each finished tile into the full C of every rank through
+          peer-mapped memory (the all-gather is fused into the epilogue); strong scaling.
+`value` is timed with CUDA events on the launching stream with inputs resident in HBM; `e2e` is
+the same product through the operator API from pinned host buffers, copies inside the timed
+region. `--impl reference` times the CPU restatement of the same product on the host cores (the
+reference project ships no matmul of its own to run).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+NOMINAL_TFLOPS = 2250.0
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (None until a capture of that kernel exists).
+NCU_TRAFFIC = {
+    "gemm_f16_4096": 82.5e6,  # profiles/gemm_tc_f16_4096_1cta.md (69.6 MB read + 12.9 MB written)
+    "int4_gemv_m1": None,
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["_source"] = "fallback"
+    return p
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()  # exact PID of the sampler this object started
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float):
+        rows = []
+        for ts, line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                rows.append((ts, float(parts[0]), float(parts[1]), float(parts[2]), parts[3:7]))
+            except ValueError:
+                continue
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        inside = [r for r in rows if t0 <= r[0] <= t1]
+        if len(inside) < 3:  # short region: fall back to the samples taken under load
+            peak_power = max(r[3] for r in rows)
+            inside = [r for r in rows if r[3] >= 0.6 * peak_power] or rows
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in inside for i in range(4) if r[4][i].lower().startswith("active")})
+        return {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": max(r[2] for r in inside),
+                "power_w_max": max(r[3] for r in inside), "reasons": reasons, "samples": len(inside)}
+
+
+# ----------------------------------------------------------------------------- helpers
+def dist_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def time_region(torch, dist, world, fn, steps, warmup):
+    """Runs `warmup` untimed and exactly `steps` timed calls of fn(i); returns ms (max over ranks)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    t1 = time.time()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, t0, t1
+
+
+def synth_f16(shape, std, seed, stream, dtype):
+    """Seeded normal(0, std) in 16-bit storage; large matrices tile a 4096 x 4096 seeded block."""
+    import numpy as np
+    import torch
+    from beantensor_b200 import synth
+    r, c = shape
+    br, bc = min(r, 4096), min(c, 4096)
+    block = synth.normal((br, bc), std, seed, stream).astype(np.float32)
+    t = torch.from_numpy(block).to(dtype)
+    if (br, bc) != (r, c):
+        t = t.repeat((r + br - 1) // br, (c + bc - 1) // bc)[:r, :c].contiguous()
+    return t
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_gemm_sample(target_seconds: float, max_rows: int = 4096):
+    """Times the CPU restatement (fp32, threaded) on a row slab of the 4096^3 product.
+    Returns (tflops, cores, sample description, seconds per call, rows)."""
+    import numpy as np
+    from beantensor_b200 import synth
+    from oracle import oracle as O
+    O.build()
+    cores = O.threads()
+    K = N = 4096
+    B = synth.normal((K, N), 1 / 64, 1, 1).astype(np.float16).astype(np.float32)
+    probe_rows = 256
+    A = synth.normal((max_rows, K), 1 / 64, 1, 0).astype(np.float16).astype(np.float32)
+    O.gemm_f32_threads(A[:probe_rows], B, cores)
+    t = time.time()
+    O.gemm_f32_threads(A[:probe_rows], B, cores)
+    per_row = (time.time() - t) / probe_rows
+    rows = int(min(max_rows, max(probe_rows, target_seconds / max(per_row, 1e-9))))
+    rows -= rows % 64
+    rows = max(rows, 64)
+    return A, B, rows, cores
+
+
+def run_reference_arm(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as O
+    total = args.steps + args.warmup
+    budget = 150.0  # seconds for the whole run
+    A, B, rows, cores = cpu_gemm_sample(budget / max(total, 1))
+    for _ in range(args.warmup):
+        O.gemm_f32_threads(A[:rows], B, cores)
+    t0 = time.time()
+    for _ in range(args.steps):
+        O.gemm_f32_threads(A[:rows], B, cores)
+    dt = time.time() - t0
+    flops = 2.0 * rows * 4096 * 4096 * args.steps
+    tflops = flops / dt / 1e12
+    sample = f"{rows} of 4096 rows of the fp16 4096^3 product per step (inputs widened to fp32), {args.steps} steps"
+    line = {
+        "impl": "reference", "metric": "fp16 GEMM TFLOP/s (4096^3) + int4 GEMV HBM GB/s", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / max(args.steps, 1) * 1e3,
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "fp16 dense GEMM M=N=K=4096 (CPU restatement; the reference ships no matmul)"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm, N = 1
+def bench_gemm_single(torch, ops, dtype, n, steps, warmup, sets, dist=None, world=1):
+    std = n ** -0.5
+    bufs = []
+    for s in range(sets):
+        a = synth_f16((n, n), std, 1, 2 * s, dtype).cuda()
+        b = synth_f16((n, n), std, 1, 2 * s + 1, dtype).cuda()
+        c = torch.empty((n, n), dtype=dtype, device="cuda")
+        bufs.append((a, b, c))
+
+    def step(i):
+        a, b, c = bufs[i % sets]
+        ops.matmul_gpu(a, b, c)
+
+    ms, t0, t1 = time_region(torch, dist, world, step, steps, warmup)
+    ops.check_device_status(torch.cuda.current_device())
+    return ms, t0, t1, bufs
+
+
+def bench_e2e_gemm(torch, ops, dtype, n, steps, warmup):
+    """Host buffers in pinned memory -> device -> product -> host, every step."""
+    std = n ** -0.5
+    ha = synth_f16((n, n), std, 1, 0, dtype).pin_memory()
+    hb = synth_f16((n, n), std, 1, 1, dtype).pin_memory()
+    hc = torch.empty((n, n), dtype=dtype).pin_memory()
+    da, db, dc = (torch.empty((n, n), dtype=dtype, device="cuda") for _ in range(3))
+
+    def step(i):
+        da.copy_(ha, non_blocking=True)
+        db.copy_(hb, non_blocking=True)
+        ops.matmul_gpu(da, db, dc)
+        hc.copy_(dc, non_blocking=True)
+
+    ms, _, _ = time_region(torch, None, 1, step, steps, warmup)
+    return ms, 2 * n * n * 2, n * n * 2
+
+
+def bench_int4(torch, ops, peaks, M, steps, warmup):
+    import numpy as np
+    from beantensor_b200 import synth
+    N, K, G = 11008, 4096, 128
+    w_bytes = N * K // 2
+    sets = max(2, (2 * L2_BYTES) // w_bytes + 1)  # rotate weight copies so every launch streams from HBM
+    w = synth.pack_int4(synth.int4((N, K), 2))
+    s = synth.uniform((N, K // G), 0.005, 0.02, 2, 1).astype(np.float16)
+    act = synth.normal((M, K), 1.0, 2, 2).astype(np.float16)
+    ws = [torch.from_numpy(w).cuda() for _ in range(sets)]
+    ss = [torch.from_numpy(s).cuda() for _ in range(sets)]
+    a = torch.from_numpy(act).cuda()
+    out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+
+    def step(i):
+        ops.matmul_int4_gpu(a, ws[i % sets], ss[i % sets], out, G)
+
+    ms, _, _ = time_region(torch, None, 1, step, steps, warmup)
+    us = ms / steps * 1e3
+    algo = w_bytes + N * (K // G) * 2 + M * K * 2 + M * N * 2
+    gbs = algo / (us * 1e-6) / 1e9
+    return {"workload": f"int4 weight-only matmul M={M} N=11008 K=4096 group=128", "us_per_launch": us,
+            "algorithmic_bytes": algo, "value": gbs, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "frac_nominal": gbs / NOMINAL_HBM_GBS,
+                         "traffic": NCU_TRAFFIC["int4_gemv_m1"] if M == 1 else None},
+            "l2": f"{sets} rotating weight copies ({sets * w_bytes >> 20} MiB > L2)"}
+
+
+def bench_bmm(torch, ops, peaks, steps, warmup):
+    Bn, M, N, K = 64, 512, 512, 128
+    sets = 6  # 6 x 48 MiB > L2
+    bufs = []
+    for s in range(sets):
+        a = synth_f16((Bn * M, K), K ** -0.5, 3, 2 * s, torch.float16).view(Bn, M, K).cuda()
+        b = synth_f16((Bn * K, N), K ** -0.5, 3, 2 * s + 1, torch.float16).view(Bn, K, N).cuda()
+        bufs.append((a, b, torch.empty((Bn, M, N), dtype=torch.float16, device="cuda")))
+
+    def step(i):
+        a, b, c = bufs[i % sets]
+        ops.bmm_gpu(a, b, c)
+
+    ms, _, _ = time_region(torch, None, 1, step, steps, warmup)
+    us = ms / steps * 1e3
+    algo = (Bn * M * K + Bn * K * N + Bn * M * N) * 2
+    gbs = algo / (us * 1e-6) / 1e9
+    tf = 2.0 * Bn * M * N * K / (us * 1e-6) / 1e12
+    return {"workload": "batched fp16 matmul [64,512,128]x[64,128,512]", "us_per_launch": us, "algorithmic_bytes": algo,
+            "value": gbs, "unit": "GB/s", "tflops": tf,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "frac_nominal": gbs / NOMINAL_HBM_GBS, "traffic": None},
+            "l2": f"{sets} rotating buffer sets ({sets * algo >> 20} MiB > L2)"}
+
+
+def bench_f32(torch, ops, steps, warmup):
+    import numpy as np
+    from beantensor_b200 import synth
+    n = 1024
+    a = torch.from_numpy(synth.uniform((n, n), -1, 1, 0, 0).astype(np.float32)).cuda()
+    b = torch.from_numpy(synth.uniform((n, n), -1, 1, 0, 1).astype(np.float32)).cuda()
+    c = torch.empty((n, n), dtype=torch.float32, device="cuda")
+    ms, _, _ = time_region(torch, None, 1, lambda i: ops.matmul_gpu(a, b, c), steps, warmup)
+    us = ms / steps * 1e3
+    return {"workload": "fp32 dense matmul M=N=K=1024 (3xTF32 split)", "us_per_launch": us,
+            "value": 2.0 * n ** 3 / (us * 1e-6) / 1e12, "unit": "TFLOP/s", "launches_per_step": 3}
+
+
+def run_single(args, peaks):
+    import torch
+    from beantensor_b200 import ops
+    torch.cuda.set_device(0)
+    ops.init(0)
+    n = 4096
+    flops = 2.0 * n ** 3
+    sets = 4  # 4 x 96 MiB of A, B, C > 126 MiB L2
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms, t0, t1, bufs = bench_gemm_single(torch, ops, torch.float16, n, args.steps, args.warmup, sets)
+    clocks = sampler.summary(t0, t1)
+    ms_step = ms / args.steps
+    tflops = flops / (ms_step * 1e-3) / 1e12
+    del bufs
+    torch.cuda.empty_cache()
+
+    e2e_steps = max(3, min(args.steps, 20))
+    e2e_ms, h2d, d2h = bench_e2e_gemm(torch, ops, torch.float16, n, e2e_steps, 3)
+    e2e_tflops = flops / (e2e_ms / e2e_steps * 1e-3) / 1e12
+
+    extra = []
+    if not args.headline_only:
+        sub_steps = max(20, min(args.steps, 400))
+        for M in (1, 8, 64):
+            extra.append(bench_int4(torch, ops, peaks, M, sub_steps, 10))
+        extra.append(bench_bmm(torch, ops, peaks, sub_steps, 10))
+        extra.append(bench_f32(torch, ops, sub_steps, 10))
+        big_steps = 5
+        msb, _, _, bb = bench_gemm_single(torch, ops, torch.bfloat16, 16384, big_steps, 3, 1)
+        tfb = 2.0 * 16384 ** 3 / (msb / big_steps * 1e-3) / 1e12
+        extra.append({"workload": "bf16 dense GEMM M=N=K=16384, 1 GPU", "ms_per_launch": msb / big_steps, "value": tfb,
+                      "unit": "TFLOP/s",
+                      "roofline": {"bound": "tensor", "achieved": tfb, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                                   "frac": tfb / peaks["bf16_tflops_sustained"], "frac_nominal": tfb / NOMINAL_TFLOPS, "traffic": None}})
+        del bb
+        torch.cuda.empty_cache()
+    sampler.stop()
+
+    cpu = None
+    if not args.no_cpu:
+        from oracle import oracle as O
+        A, B, rows, cores = cpu_gemm_sample(8.0)
+        O.gemm_f32_threads(A[:rows], B, cores)
+        t = time.time()
+        O.gemm_f32_threads(A[:rows], B, cores)
+        dt = time.time() - t
+        cpu = {"value": 2.0 * rows * 4096 * 4096 / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+               "sample": f"{rows} of 4096 rows of the fp16 4096^3 product, inputs widened to fp32, one timed run of {dt:.1f} s "
+                         "(CPU restatement; the reference ships no matmul)"}
+
+    line = {
+        "metric": "fp16 GEMM TFLOP/s (4096^3) + int4 GEMV HBM GB/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "fp16 dense GEMM M=N=K=4096, row-major A[M,K] B[K,N], fp32 accumulate, fp16 out",
+                   "l2": f"{sets} rotating A/B/C sets ({sets * 96} MiB > 126 MiB L2)", "tile": "128x256x64, 4-stage TMA ring, 1 CTA/SM"},
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": tflops / peaks["bf16_tflops"], "frac_nominal": tflops / NOMINAL_TFLOPS,
+                     "peak_source": peaks["_source"] + " cuBLAS bf16 burst", "traffic": NCU_TRAFFIC["gemm_f16_4096"]},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "configs": extra,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm, N > 1
+def run_multi(args, peaks):
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from beantensor_b200 import _lib, ops
+    from beantensor_b200.errors import raise_for_status
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ops.init(local_rank)
+    L = _lib.lib()
+    n = 16384
+    nloc = n // world
+    dtype = torch.bfloat16
+    a = synth_f16((n, n), n ** -0.5, 4, 0, dtype).cuda()
+    b_full_block = synth_f16((n, nloc), n ** -0.5, 4, 1 + rank, dtype).cuda()
+
+    # Full C of every rank lives in IPC-exportable memory so that peers can store into it.
+    ptr = C.c_void_p()
+    handle = C.create_string_buffer(64)
+    raise_for_status(L.btm_ipc_alloc(local_rank, n * n * 2, C.byref(ptr), handle))
+    handles = [None] * world
+    dist.all_gather_object(handles, handle.raw)
+    peers = []
+    for r in range(world):
+        if r == rank:
+            peers.append(ptr.value)
+        else:
+            p = C.c_void_p()
+            raise_for_status(L.btm_ipc_open(local_rank, handles[r], C.byref(p)))
+            peers.append(p.value)
+    table = (C.c_void_p * world)(*peers)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def step(i):
+        raise_for_status(L.btm_gemm_nshard(local_rank, stream, _lib.BF16, n, nloc, n, a.data_ptr(), n, b_full_block.data_ptr(), nloc,
+                                           table, n, rank, world))
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, t0, t1 = time_region(torch, dist, world, step, args.steps, args.warmup)
+    ops.check_device_status(local_rank)
+    clocks = sampler.summary(t0, t1) if rank == 0 else None
+    if rank == 0:
+        sampler.stop()
+    ms_step = ms / args.steps
+    flops = 2.0 * n ** 3
+    tflops = flops / (ms_step * 1e-3) / 1e12
+
+    # End to end: A and the local B block from pinned host memory, full C back to the host.
+    ha, hb = a.cpu().pin_memory(), b_full_block.cpu().pin_memory()
+    hc = torch.empty((n, n), dtype=dtype).pin_memory()
+    c_dev = _wrap_device_memory(torch, ptr.value, (n, n)).view(dtype)
+
+    def e2e_step(i):
+        a.copy_(ha, non_blocking=True)
+        b_full_block.copy_(hb, non_blocking=True)
+        step(i)
+        dist.barrier()  # every peer's tiles have landed in this rank's C
+        hc.copy_(c_dev, non_blocking=True)
+
+    e2e_steps = 3
+    e2e_ms, _, _ = time_region(torch, dist, world, e2e_step, e2e_steps, 1)
+    e2e_tflops = flops / (e2e_ms / e2e_steps * 1e-3) / 1e12
+
+    if rank == 0:
+        line = {
+            "metric": "fp16 GEMM TFLOP/s (4096^3) + int4 GEMV HBM GB/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded 4096^2 blocks tiled)",
+            "config": {"workload": f"bf16 GEMM M=N=K=16384, B split by N-columns over {world} ranks, all-gather of C fused into the epilogue "
+                                   "(peer stores over NVLink)", "l2": "inputs (1 GiB+) exceed L2", "parallelism": f"nshard{world}"},
+            "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s per GPU",
+                         "frac": tflops / world / peaks["bf16_tflops_sustained"], "frac_nominal": tflops / world / NOMINAL_TFLOPS,
+                         "peak_source": peaks["_source"] + " cuBLAS bf16 sustained", "traffic": None},
+            "cpu_baseline": None,
+            "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": (n * n + n * nloc) * 2, "d2h_bytes_per_step": n * n * 2,
+                    "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    for r in range(world):
+        if r != rank:
+            L.btm_ipc_close(local_rank, C.c_void_p(peers[r]))
+    dist.barrier()
+    L.btm_ipc_free(local_rank, ptr)
+    dist.destroy_process_group()
+
+
+class _RawCuda:
+    """Zero-copy view of library-owned device memory for torch (CUDA array interface, 16-bit words)."""
+
+    def __init__(self, ptr, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<i2", "data": (int(ptr), False), "version": 2}
+
+
+def _wrap_device_memory(torch, ptr, shape):
+    return torch.as_tensor(_RawCuda(ptr, shape), device="cuda")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--headline-only", action="store_true", help="skip the secondary workloads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    _, _, world = dist_env()
+    if args.impl == "reference":
+        args.steps = args.steps if args.steps is not None else 5
+        args.warmup = args.warmup if args.warmup is not None else 1
+        run_reference_arm(args)
+        return
+    multi = world > 1 or args.gpus > 1
+    if args.steps is None:
+        args.steps = 20 if multi else 2000
+    if args.warmup is None:
+        args.warmup = 3 if multi else 20
+    args.warmup = max(args.warmup, 3)
+    peaks = load_peaks()
+    if multi:
+        if world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run); WORLD_SIZE={world}")
+        run_multi(args, peaks)
+    else:
+        run_single(args, peaks)
+
+
+if __name__ == "__main__":
+    main()
