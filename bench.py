@@ -399,8 +399,10 @@ def run_multi(args, peaks):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ops.init(local_rank)
     L = _lib.lib()
+    from beantensor_b200 import sharding
     n = 16384
-    nloc = n // world
+    c_lo, c_hi = sharding.column_block(n, rank, world)
+    nloc = c_hi - c_lo
     dtype = torch.bfloat16
     a = synth_f16((n, n), n ** -0.5, 4, 0, dtype).cuda()
     b_full_block = synth_f16((n, nloc), n ** -0.5, 4, 1 + rank, dtype).cuda()
