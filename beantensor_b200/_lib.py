@@ -25,6 +25,7 @@ SIGNATURES = {
     "btm_gemm": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
     "btm_gemm_f32_workspace_bytes": (_sz, [_i, _i, _i]),
     "btm_gemm_f32_ws": (_i, [_i, _vp, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _sz]),
+    "btm_gemm_f32_static": (_i, [_i, _vp, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
     "btm_bmm": (_i, [_i, _vp, _i, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
     "btm_int4_matmul": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "btm_int4_dequant": (_i, [_i, _vp, _i, _i, _i, _vp, _vp, _vp]),

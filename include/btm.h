@@ -124,6 +124,27 @@ size_t btm_gemm_f32_workspace_bytes(int M, int N, int K);
 int btm_gemm_f32_ws(int device, void *stream, int M, int N, int K, const void *A, int64_t lda, const void *B,
                     int64_t ldb, void *C, int64_t ldc, void *workspace, size_t workspace_bytes);
 
+/* fp32 matmul for callers that cannot allocate. No counterpart in the reference (it has no matmul,
+ * and its operators allocate freely, e.g. Tensor/TensorOps.cu:248,329-333).
+ * Who needs it: a worker that runs while another thread owns the CUDA allocator, a host that gave
+ * all device memory to its own pool at start-up, a service with a fixed, audited memory budget. For
+ * them btm_gemm(BTM_F32) is unusable because it grows its scratch with cudaMalloc. This call does the
+ * same three-term TF32 product with the operand planes in a fixed array inside the library image:
+ * it never calls cudaMalloc, cudaFree or any allocating routine.
+ * Limits and rules:
+ *   - (M + N) * roundup(K,4) * 8 bytes must not exceed BTM_STATIC_SCRATCH_BYTES (64 MiB, e.g. up to
+ *     2048^3); larger products return BTM_ERR_UNSUPPORTED with a message that says so. Every GPU
+ *     that loads the library holds those 64 MiB until the process exits.
+ *   - all calls on a device share the one array: calls whose kernels can overlap on the GPU
+ *     (different streams, unordered host threads) race on it. Order them on one stream.
+ *   - the first call on a device looks up the array's device address (once per device); make that
+ *     first call before starting any stream capture.
+ *   - a kernel wait that ran out is reported by a later call of this function on the same device
+ *     (BTM_ERR_TIMEOUT), checked only when `stream` is idle. */
+#define BTM_STATIC_SCRATCH_BYTES (64ull << 20)
+int btm_gemm_f32_static(int device, void *stream, int M, int N, int K, const void *A, int64_t lda, const void *B,
+                        int64_t ldb, void *C, int64_t ldc);
+
 /* Batched matmul: `batch` independent products C[b] = A[b] . B[b] with element strides
  * between consecutive matrices; each matrix is row-major and dense (lda=K, ldb=N, ldc=N).
  * The reference has no such op (not even a stub); it extends Ops/Algebra/MatMul the same
