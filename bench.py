@@ -323,11 +323,11 @@ def run_single(args, peaks):
     from beantensor_b200 import ops
     torch.cuda.set_device(0)
     ops.init(0)
+    sampler = ClockSampler(0)
+    sampler.start()  # nvidia-smi needs a moment to come up: start it before the inputs are built
     n = 4096
     flops = 2.0 * n ** 3
     sets = 4  # 4 x 96 MiB of A, B, C > 126 MiB L2
-    sampler = ClockSampler(0)
-    sampler.start()
     ms, t0, t1, bufs = bench_gemm_single(torch, ops, torch.float16, n, args.steps, args.warmup, sets)
     clocks = sampler.summary(t0, t1)
     ms_step = ms / args.steps
@@ -399,6 +399,9 @@ def run_multi(args, peaks):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ops.init(local_rank)
     L = _lib.lib()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to come up: start it before the inputs are built
     from beantensor_b200 import sharding
     n = 16384
     c_lo, c_hi = sharding.column_block(n, rank, world)
@@ -428,9 +431,6 @@ def run_multi(args, peaks):
         raise_for_status(L.btm_gemm_nshard(local_rank, stream, _lib.BF16, n, nloc, n, a.data_ptr(), n, b_full_block.data_ptr(), nloc,
                                            table, n, rank, world))
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     ms, t0, t1 = time_region(torch, dist, world, step, args.steps, args.warmup)
     ops.check_device_status(local_rank)
     clocks = sampler.summary(t0, t1) if rank == 0 else None
