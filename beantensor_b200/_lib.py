@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libbtm.so")
+LIB_PATH = os.environ.get("BTM_LIB") or os.path.join(HERE, "libbtm.so")  # BTM_LIB: load another build of the library
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT = range(7)
 BF16, F16, F32, F64, I64, I32, I16, I8, U64, U32, U16, U8, INT4X2 = range(13)  # Tensor/Dtypes.h:57-70 + appended int4
@@ -23,6 +23,7 @@ SIGNATURES = {
     "btm_init": (_i, [_i]),
     "btm_check_device_status": (_i, [_i, _vp]),
     "btm_gemm": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "btm_gemm_bt": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
     "btm_gemm_f32_workspace_bytes": (_sz, [_i, _i, _i]),
     "btm_gemm_f32_ws": (_i, [_i, _vp, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _sz]),
     "btm_gemm_f32_static": (_i, [_i, _vp, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),

@@ -2,6 +2,7 @@
 // kernels. Nothing here computes on the CPU; every path ends in a CUDA launch or an error.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -78,6 +79,7 @@ DeviceState *device_state(int device)
     if (check_cuda(cudaMalloc(&ds->status, sizeof(int)), "cudaMalloc(status)")) return nullptr;
     if (check_cuda(cudaMemset(ds->status, 0, sizeof(int)), "cudaMemset(status)")) return nullptr;
     if (configure_gemm_tc_kernels()) return nullptr;
+    if (configure_gemm_tc2_kernels()) return nullptr;
     ds->sm_count = prop.multiProcessorCount;
     ds->ws = nullptr;
     ds->ws_bytes = 0;
@@ -162,6 +164,16 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
     p.col0 = c.col0;
     p.c_vec_ok = vec ? 1 : 0;
     p.status = ds->status;
+    // CTA pairs (256 x 256 tiles, B shared between two SMs) once there is enough work to fill a good
+    // part of the machine; single CTAs (128 x 256 or 128 x 128) for small outputs.
+    // BTM_FORCE_KERNEL=1cta|2cta overrides the choice (used by the tests to cover both on every shape).
+    const long long pair_tiles = (long long)c.batch * ((c.M + 255) / 256) * ((c.N + 255) / 256);
+    bool pair = c.M > 128 && pair_tiles >= ds->sm_count / 4;
+    if (const char *force = getenv("BTM_FORCE_KERNEL")) {
+        if (!strcmp(force, "1cta")) pair = false;
+        else if (!strcmp(force, "2cta")) pair = true;
+    }
+    if (pair) return launch_gemm_tc2(c.dtype, st, ds->sm_count, tmA, tmB, p);
     return launch_gemm_tc(c.dtype, st, ds->sm_count, tmA, tmB, p, 0);
 }
 
@@ -338,6 +350,37 @@ int btm_bmm(int device, void *stream, int dtype, int batch, int M, int N, int K,
     c.A = A; c.B = B; c.lda = K; c.ldb = N; c.strideA = strideA; c.strideB = strideB;
     c.C[0] = C; c.ndst = 1; c.ldc = N; c.strideC = strideC;
     return run_16bit(ds, (cudaStream_t)stream, c);
+}
+
+int btm_gemm_bt(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *Bt, int64_t ldbt,
+                void *C, int64_t ldc)
+{
+    if (dtype != BTM_F16 && dtype != BTM_BF16)
+        return set_error(BTM_ERR_UNSUPPORTED, "matmul with transposed B: dtype %d is not supported (Float16, BFloat16 only)", dtype);
+    int rc = check_gemm_args(dtype, M, N, K, A, lda, Bt, N /* checked below */, C, ldc);
+    if (rc) return rc;
+    if (ldbt < K) return set_error(BTM_ERR_INVALID, "matmul with transposed B: ldbt=%lld is smaller than K=%d", (long long)ldbt, K);
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    if (M == 0 || N == 0) return BTM_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t es = 2;
+    if (K == 0 || !tma_ok(A, lda, 0, 1, es) || !tma_ok(Bt, ldbt, 0, 1, es))
+        return set_error(BTM_ERR_UNSUPPORTED, "matmul with transposed B: operands must be 16-byte aligned with 16-byte row pitch and K > 0");
+    const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+    const int bn = t256 < ds->sm_count ? 128 : 256;
+    CUtensorMap tmA, tmB;
+    rc = encode_tmap_3d(&tmA, dtype, A, (uint64_t)K, (uint64_t)M, 1, (uint64_t)lda * es, (uint64_t)lda * es, 64, 128);
+    if (rc) return rc;
+    rc = encode_tmap_3d(&tmB, dtype, Bt, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldbt * es, (uint64_t)ldbt * es, 64, (uint32_t)bn);
+    if (rc) return rc;
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = M; p.N = N; p.K = K; p.batch = 1; p.group_m = 8; p.ndst = 1;
+    p.C[0] = C; p.ldc = ldc;
+    p.c_vec_ok = (aligned16(C) && (ldc * (long long)es) % 16 == 0) ? 1 : 0;
+    p.status = ds->status;
+    return launch_gemm_tc_bt(dtype, st, ds->sm_count, tmA, tmB, p, bn);
 }
 
 int btm_gemm_nshard(int device, void *stream, int dtype, int M, int Nloc, int K, const void *A, int64_t lda,

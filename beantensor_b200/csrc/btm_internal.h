@@ -16,6 +16,8 @@ struct GemmParams {
     int batch;           // independent products (1 for plain matmul)
     int tiles_m, tiles_n; // tiles per product
     int num_kb;          // k-blocks per tile
+    int tiles_full;      // two-SM kernel: tiles of full width in the list ...
+    int tiles_tail;      // ... followed by this many half-width tiles
     int group_m;         // tile raster: m-tiles per L2 group
     void *C[kMaxDst];    // output bases; [0] is local, others are peer-mapped copies of C
     int ndst;
@@ -46,6 +48,8 @@ int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, u
 // Launchers (defined next to their kernels). All return a btm_status.
 int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB,
                    const GemmParams &p, int force_bn);
+int launch_gemm_tc_bt(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB,
+                      const GemmParams &p, int bn);
 int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K, const void *A, long long lda,
                      long long strideA, const void *B, long long ldb, long long strideB, void *C, long long ldc,
                      long long strideC);
@@ -58,5 +62,7 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
 int launch_int4_dequant(cudaStream_t st, int N, int K, int group, const void *w, const void *scales, void *out);
 int launch_int4_unpack(cudaStream_t st, int N, int K, const void *w, void *out);
 int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once per device
+int configure_gemm_tc2_kernels();
+int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p);
 
 } // namespace btm

@@ -27,7 +27,7 @@ constexpr int SLICE_BYTES = 128; // bytes of K (for A) or N (for B) per shared-m
 constexpr int UMMA_K_BYTES = 32; // bytes of K consumed by one tcgen05.mma
 constexpr int NUM_THREADS = 192;
 
-template <int BN, int DT>
+template <int BN, int DT, bool BT = false>
 struct TileCfg {
     static constexpr bool kTf32 = (DT == BTM_F32);
     static constexpr int kEs = kTf32 ? 4 : 2;              // element bytes
@@ -36,7 +36,7 @@ struct TileCfg {
     // 16-bit B stays row-major [K,N] in global memory and is consumed MN-major: BN/64 chunks of
     // kBKE rows x 128 B. The fp32 planes are written transposed ([N,K]) by the split pass, so B
     // is K-major like A: BN rows x 128 B from a single TMA box.
-    static constexpr bool kBMnMajor = !kTf32;
+    static constexpr bool kBMnMajor = !kTf32 && !BT; // BT: the caller's B is already [N,K] (K-major)
     static constexpr int kChunkN = SLICE_BYTES / kEs;       // n elements per MN-major B chunk
     static constexpr int kChunks = BN / kChunkN;            // MN-major B chunks per stage
     static constexpr int kChunkBytes = kBKE * SLICE_BYTES;  // one MN-major chunk: kBKE rows of 128 B
@@ -52,11 +52,20 @@ struct TileCfg {
 };
 
 struct TileCoord {
-    int b, m, n;
+    int b, m, n0, bn; // product, row-tile index, first column, width (BN, or BN/2 for a tail tile)
 };
 
-__device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int tile)
+// The tile list is `tiles_full` full-width tiles followed by `tiles_tail` half-width ones: the tiles
+// of a partly filled last wave are run as twice as many half tiles, which halves the tail.
+template <int BN>
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int tile_in_list)
 {
+    int tile = tile_in_list, half = -1;
+    if (tile_in_list >= p.tiles_full) {
+        const int s = tile_in_list - p.tiles_full;
+        tile = p.tiles_full + (s >> 1);
+        half = s & 1;
+    }
     const int per_batch = p.tiles_m * p.tiles_n;
     TileCoord c;
     c.b = tile / per_batch;
@@ -67,7 +76,8 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int tile)
     const int gsz = min(p.tiles_m - first_m, p.group_m);
     const int r = t - gid * per_group;
     c.m = first_m + r % gsz;
-    c.n = r / gsz;
+    c.bn = half < 0 ? BN : BN / 2;
+    c.n0 = (r / gsz) * BN + (half > 0 ? BN / 2 : 0);
     return c;
 }
 
@@ -127,11 +137,11 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams &p, const uint3
     }
 }
 
-template <int BN, int DT>
+template <int BN, int DT, bool BT = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p)
 {
-    using Cfg = TileCfg<BN, DT>;
+    using Cfg = TileCfg<BN, DT, BT>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[Cfg::kStages];
     __shared__ __align__(8) uint64_t bar_empty[Cfg::kStages];
@@ -143,7 +153,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u; // swizzle atoms need 1024-byte alignment
-    const int total_tiles = p.batch * p.tiles_m * p.tiles_n;
+    const int total_tiles = p.tiles_full + p.tiles_tail;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -175,7 +185,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const TileCoord tc = decode_tile(p, tile);
+                const TileCoord tc = decode_tile<BN>(p, tile);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
                         ok = false;
@@ -183,7 +193,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     const uint32_t full = smem_u32(&bar_full[stage]);
                     const uint32_t sbase = smem_base + stage * Cfg::kStageBytes;
-                    mbar_expect_tx(full, Cfg::kStageBytes);
+                    // A tail tile (16-bit only) loads half of the B chunks.
+                    const int chunks = Cfg::kBMnMajor ? tc.bn / Cfg::kChunkN : 0;
+                    mbar_expect_tx(full, Cfg::kBMnMajor ? (uint32_t)(Cfg::kABytes + chunks * Cfg::kChunkBytes) : (uint32_t)Cfg::kStageBytes);
                     const int k0 = kb * Cfg::kBKE;
 #pragma unroll
                     for (int pl = 0; pl < Cfg::kPlanes; ++pl) {
@@ -193,9 +205,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         if constexpr (Cfg::kBMnMajor) {
 #pragma unroll
                             for (int c = 0; c < Cfg::kChunks; ++c)
-                                tma_load_3d(bbase + c * Cfg::kChunkBytes, &tmB, tc.n * BN + c * Cfg::kChunkN, k0, z, full);
+                                if (c < chunks) tma_load_3d(bbase + c * Cfg::kChunkBytes, &tmB, tc.n0 + c * Cfg::kChunkN, k0, z, full);
                         } else {
-                            tma_load_3d(bbase, &tmB, k0, tc.n * BN, z, full);
+                            tma_load_3d(bbase, &tmB, k0, tc.n0, z, full);
                         }
                     }
                     if (++stage == Cfg::kStages) {
@@ -208,12 +220,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(Cfg::kTf32 ? 2u : (DT == BTM_BF16 ? 1u : 0u), false, Cfg::kBMnMajor, BM, BN);
+            constexpr uint32_t kFmt = Cfg::kTf32 ? 2u : (DT == BTM_BF16 ? 1u : 0u);
+            constexpr uint32_t idesc_full = make_idesc(kFmt, false, Cfg::kBMnMajor, BM, BN);
+            constexpr uint32_t idesc_half = make_idesc(kFmt, false, Cfg::kBMnMajor, BM, BN / 2);
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+                const uint32_t idesc = tile < p.tiles_full ? idesc_full : idesc_half;
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
                 if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag, p.status, WAIT_MMA_TMEM_EMPTY)) break;
@@ -261,21 +276,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int quad = warp & 3; // tensor-memory lane quadrant this warp may read
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-            const TileCoord tc = decode_tile(p, tile);
+            const TileCoord tc = decode_tile<BN>(p, tile);
             const int acc = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-            // The verdict must be warp-uniform: tcgen05.ld below needs the whole warp.
-            const bool ready = mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL);
-            if (!__all_sync(0xffffffffu, ready)) break;
+            // One lane waits and broadcasts the verdict: tcgen05.ld below needs the whole warp.
+            if (!mbar_wait_warp(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL)) break;
             tc_fence_after();
             const int row = tc.m * BM + quad * 32 + lane;
             const long long row_off = (long long)tc.b * p.strideC + (long long)row * p.ldc + p.col0;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < tc.bn / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
                 tmem_ld_wait();
-                const int col = tc.n * BN + c * 32;
+                const int col = tc.n0 + c * 32;
                 const int valid = min(32, p.N - col);
                 if (row < p.M && valid > 0) store_row_chunk<DT>(p, v, row_off + col, valid);
             }
@@ -363,27 +377,35 @@ int launch_split_tf32(cudaStream_t st, const float *src, long long ld, int rows,
     return check_cuda(cudaGetLastError(), "split_tf32 launch");
 }
 
-template <int BN, int DT>
+template <int BN, int DT, bool BT = false>
 static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, GemmParams p)
 {
-    using Cfg = TileCfg<BN, DT>;
+    using Cfg = TileCfg<BN, DT, BT>;
     p.tiles_m = (p.M + BM - 1) / BM;
     p.tiles_n = (p.N + BN - 1) / BN;
     p.num_kb = (p.K + Cfg::kBKE - 1) / Cfg::kBKE;
     if (p.group_m <= 0) p.group_m = 8;
     const long long total = (long long)p.batch * p.tiles_m * p.tiles_n;
     if (total <= 0) return BTM_OK;
-    if (total > 0x7FFFFFFFLL) return set_error(BTM_ERR_UNSUPPORTED, "too many output tiles (%lld)", total);
-    const int grid = (int)(total < sm_count ? total : sm_count);
-    gemm_tc_kernel<BN, DT><<<grid, NUM_THREADS, Cfg::kSmemBytes, st>>>(tmA, tmB, p);
+    if (total > 0x3FFFFFFFLL) return set_error(BTM_ERR_UNSUPPORTED, "too many output tiles (%lld)", total);
+    // Tail: r = total mod SMs tiles would leave most SMs idle for a whole tile time; when 2r <= SMs
+    // they run as 2r half-width tiles instead (16-bit kernels with at least 128-column halves).
+    int tail_big = 0;
+    const int rem = (int)(total % sm_count);
+    if (Cfg::kBMnMajor && BN >= 256 && rem > 0 && 2 * rem <= sm_count) tail_big = rem;
+    p.tiles_full = (int)total - tail_big;
+    p.tiles_tail = 2 * tail_big;
+    const long long sched = (long long)p.tiles_full + p.tiles_tail;
+    const int grid = (int)(sched < sm_count ? sched : sm_count);
+    gemm_tc_kernel<BN, DT, BT><<<grid, NUM_THREADS, Cfg::kSmemBytes, st>>>(tmA, tmB, p);
     return check_cuda(cudaGetLastError(), "gemm_tc launch");
 }
 
-template <int BN, int DT>
+template <int BN, int DT, bool BT = false>
 static cudaError_t raise_smem()
 {
-    return cudaFuncSetAttribute(gemm_tc_kernel<BN, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                TileCfg<BN, DT>::kSmemBytes);
+    return cudaFuncSetAttribute(gemm_tc_kernel<BN, DT, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                TileCfg<BN, DT, BT>::kSmemBytes);
 }
 
 int configure_gemm_tc_kernels()
@@ -395,6 +417,10 @@ int configure_gemm_tc_kernels()
     if (e == cudaSuccess) e = raise_smem<128, BTM_BF16>();
     if (e == cudaSuccess) e = raise_smem<128, BTM_F32>();
     if (e == cudaSuccess) e = raise_smem<64, BTM_F32>();
+    if (e == cudaSuccess) e = raise_smem<256, BTM_F16, true>();
+    if (e == cudaSuccess) e = raise_smem<256, BTM_BF16, true>();
+    if (e == cudaSuccess) e = raise_smem<128, BTM_F16, true>();
+    if (e == cudaSuccess) e = raise_smem<128, BTM_BF16, true>();
     return check_cuda(e, "cudaFuncSetAttribute(gemm_tc)");
 }
 
@@ -423,6 +449,19 @@ int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &
     }
     if (bn == 128) return launch_one<128, BTM_BF16>(st, sm_count, tmA, tmB, p);
     return launch_one<256, BTM_BF16>(st, sm_count, tmA, tmB, p);
+}
+
+// 16-bit product with B given transposed ([N,K] row-major, i.e. K-major): C = A . Bt^T. The B box of
+// the tensor map is one whole tile (bn rows x 64 k), so the caller fixes bn (256 or 128).
+int launch_gemm_tc_bt(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB,
+                      const GemmParams &p, int bn)
+{
+    if (dtype == BTM_F16) {
+        if (bn == 128) return launch_one<128, BTM_F16, true>(st, sm_count, tmA, tmB, p);
+        return launch_one<256, BTM_F16, true>(st, sm_count, tmA, tmB, p);
+    }
+    if (bn == 128) return launch_one<128, BTM_BF16, true>(st, sm_count, tmA, tmB, p);
+    return launch_one<256, BTM_BF16, true>(st, sm_count, tmA, tmB, p);
 }
 
 } // namespace btm

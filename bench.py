@@ -325,9 +325,9 @@ def run_single(args, peaks):
     ops.init(0)
     sampler = ClockSampler(0)
     sampler.start()  # nvidia-smi needs a moment to come up: start it before the inputs are built
-    n = 4096
+    n = args.size
     flops = 2.0 * n ** 3
-    sets = 4  # 4 x 96 MiB of A, B, C > 126 MiB L2
+    sets = 4 if n <= 4096 else 2  # 4 x 96 MiB of A, B, C > 126 MiB L2
     ms, t0, t1, bufs = bench_gemm_single(torch, ops, torch.float16, n, args.steps, args.warmup, sets)
     clocks = sampler.summary(t0, t1)
     ms_step = ms / args.steps
@@ -373,8 +373,9 @@ def run_single(args, peaks):
         "metric": "fp16 GEMM TFLOP/s (4096^3) + int4 GEMV HBM GB/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "fp16 dense GEMM M=N=K=4096, row-major A[M,K] B[K,N], fp32 accumulate, fp16 out",
-                   "l2": f"{sets} rotating A/B/C sets ({sets * 96} MiB > 126 MiB L2)", "tile": "128x256x64, 4-stage TMA ring, 1 CTA/SM"},
+        "config": {"workload": f"fp16 dense GEMM M=N=K={n}, row-major A[M,K] B[K,N], fp32 accumulate, fp16 out",
+                   "l2": f"{sets} rotating A/B/C sets ({sets * 3 * n * n * 2 >> 20} MiB > 126 MiB L2)",
+                   "kernel": args.force_kernel or "library choice"},
         "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": tflops / peaks["bf16_tflops"], "frac_nominal": tflops / NOMINAL_TFLOPS,
                      "peak_source": peaks["_source"] + " cuBLAS bf16 burst", "traffic": NCU_TRAFFIC["gemm_f16_4096"]},
@@ -502,8 +503,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline-only", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--force-kernel", default=None, choices=["1cta", "2cta"],
+                    help="pin the 16-bit matmul to the one-CTA or the two-SM kernel (default: the library chooses)")
+    ap.add_argument("--size", type=int, default=4096, help="M=N=K of the headline product (profiling aid; the metric is quoted at 4096)")
     args = ap.parse_args()
     _, _, world = dist_env()
+    if args.force_kernel:
+        os.environ["BTM_FORCE_KERNEL"] = args.force_kernel
     if args.impl == "reference":
         args.steps = args.steps if args.steps is not None else 5
         args.warmup = args.warmup if args.warmup is not None else 1

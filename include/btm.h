@@ -117,6 +117,14 @@ int btm_check_device_status(int device, void *stream);
 int btm_gemm(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B,
              int64_t ldb, void *C, int64_t ldc);
 
+/* C[M,N] = A[M,K] . Bt[N,K]^T: the same product with B supplied transposed (row-major [N,K], so both
+ * operands are K-contiguous). This is the copy-free form of matmul(a, transpose(b)); the reference's
+ * Ops/Algebra/Transpose is an empty stub (Ops/Algebra/Transpose/Transpose.h), so a BeanTensor
+ * caller would otherwise have to materialise the transpose. BTM_F16 / BTM_BF16, tensor-core path only:
+ * bases and row pitches must be multiples of 16 bytes and K > 0, else BTM_ERR_UNSUPPORTED. */
+int btm_gemm_bt(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *Bt,
+                int64_t ldbt, void *C, int64_t ldc);
+
 /* Same product for BTM_F32 with caller-owned scratch instead of the library's:
  * `workspace` is device memory of at least btm_gemm_f32_workspace_bytes(M,N,K) bytes,
  * 256-byte aligned. Nothing is allocated. */

@@ -137,3 +137,36 @@ def test_repeatable(btm):
     btm.matmul_gpu(a, b, o1)
     btm.matmul_gpu(a, b, o2)
     assert torch.equal(o1, o2)
+
+
+@pytest.mark.parametrize("kernel", ["1cta", "2cta"])
+@pytest.mark.parametrize("dtype", [_lib.F16, _lib.BF16])
+def test_both_tensor_core_kernels_on_ragged_and_tail_shapes(btm, oracle, dtype, kernel, monkeypatch):
+    # The library picks between single CTAs and CTA pairs by size; pin each in turn. The shapes
+    # include ones whose last wave is split into half-width tiles (e.g. 38 or 75 full tiles).
+    monkeypatch.setenv("BTM_FORCE_KERNEL", kernel)
+    for (M, N, K) in [(256, 256, 64), (130, 72, 40), (1000, 1000, 992), (2432, 4096, 128), (384, 6400, 192), (257, 513, 136)]:
+        err, _, _ = run_case(btm, oracle, dtype, M, N, K, seed=M + N + K)
+        assert err <= TOL[dtype], (kernel, (M, N, K), err)
+
+
+@pytest.mark.parametrize("dtype", [_lib.F16, _lib.BF16])
+def test_transposed_b_entry_point(btm, oracle, dtype):
+    # btm_gemm_bt: C = A . Bt^T with Bt stored [N,K]; compared with the oracle on B = Bt^T.
+    import ctypes as C
+    import torch
+    L = _lib.lib()
+    for (M, N, K) in [(128, 256, 64), (300, 520, 200), (1024, 1024, 1024), (129, 8, 72)]:
+        A, B = gemm_inputs(dtype, M, N, K, 5)
+        Bt = np.ascontiguousarray(B.T)
+        a, bt = to_gpu(A, dtype), to_gpu(Bt, dtype)
+        out = torch.full((M, N), float("nan"), dtype=torch_dtype(dtype), device="cuda")
+        rc = L.btm_gemm_bt(0, C.c_void_p(torch.cuda.current_stream().cuda_stream), dtype, M, N, K, a.data_ptr(), K, bt.data_ptr(), K,
+                           out.data_ptr(), N)
+        assert rc == _lib.OK, _lib.last_error()
+        btm.check_device_status(0)
+        assert oracle.rel_frobenius(to_host_bits(out, dtype), dtype, oracle.gemm(dtype, A, B)) <= TOL[dtype], (M, N, K)
+    # unaligned pitch is refused, not silently mishandled
+    a = torch.zeros((8, 12), dtype=torch_dtype(dtype), device="cuda")
+    rc = L.btm_gemm_bt(0, None, dtype, 8, 8, 12, a.data_ptr(), 12, a.data_ptr(), 12, a.data_ptr(), 8)
+    assert rc == _lib.ERR_UNSUPPORTED
