@@ -420,7 +420,7 @@ int btm_int4_matmul(int device, void *stream, int M, int N, int K, int group, co
         return set_error(BTM_ERR_INVALID, "int4 matmul: null pointer");
     DeviceState *ds = device_state(device);
     if (!ds) return last_code();
-    return launch_int4_gemv((cudaStream_t)stream, ds->sm_count, M, N, K, group, act_f16, w_packed, scales_f16, out_f16);
+    return launch_int4_gemv((cudaStream_t)stream, ds->sm_count, M, N, K, group, act_f16, w_packed, scales_f16, out_f16, ds->status);
 }
 
 int btm_int4_dequant(int device, void *stream, int N, int K, int group, const void *w_packed, const void *scales_f16,

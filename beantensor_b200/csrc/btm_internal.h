@@ -58,7 +58,7 @@ int launch_split_tf32(cudaStream_t st, const float *src, long long ld, int rows,
 int launch_split_tf32_transpose(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
                                 float *dst_lo, long long ld_dst);
 int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act,
-                     const void *w, const void *scales, void *out);
+                     const void *w, const void *scales, void *out, int *status);
 int launch_int4_dequant(cudaStream_t st, int N, int K, int group, const void *w, const void *scales, void *out);
 int launch_int4_unpack(cudaStream_t st, int N, int K, const void *w, void *out);
 int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once per device

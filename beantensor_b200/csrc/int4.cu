@@ -5,33 +5,25 @@
 // odd k in bits 4-7; one fp16 scale per `group` consecutive k, row-major [N, K/group].
 //
 // int4_gemv_kernel (M <= 8 per launch row-block) is a weight-streaming kernel: the packed
-// weights are read exactly once with 128-bit loads, unpacked to exact fp16 integers in
-// registers, and multiplied with the activations by mma.sync m16n8k16 (16 weight rows x 8
+// weights are read from HBM exactly once (bulk async copies into shared memory, issued for the
+// CTA's whole slab at once), then fetched with 128-bit shared loads, unpacked to exact fp16 integers
+// in registers, and multiplied with the activations by mma.sync m16n8k16 (16 weight rows x 8
 // activation rows per instruction, fp32 accumulation). Per 128-k block the fp32 partial sums
 // are multiplied by the group scale and added to the running total, so the arithmetic is
 //   out[m,n] = f16_rne( sum_g float(S[n,g]) * sum_{k in g} float(act[m,k]) * W[n,k] ).
 // The sum over k inside an mma is order-free, which lets every lane keep the 32 consecutive
 // nibbles of one 128-bit load: lane (g,t) of a warp owns weight rows g and g+8 and the k range
-// [t*32, t*32+32) of each 128-k block; activations are staged in shared memory already permuted
-// into the matching slot order.
+// [t*32, t*32+32) of each 128-k block; the matching activations are read from global memory (L1
+// hits after the first touch) and permuted into the same slot order with two byte-permutes per pair.
 #include <cuda_fp16.h>
 
 #include "btm_internal.h"
+#include "btm_ptx.cuh"
 
 namespace btm {
 
 constexpr int GEMV_ROWS = 16;   // weight rows per CTA (= mma M)
 constexpr int GEMV_WARPS = 4;   // 128-k blocks are dealt round-robin to the warps
-constexpr int GEMV_UNROLL = 4;  // 128-k blocks in flight per warp
-
-__device__ __forceinline__ uint4 ldg_stream(const uint4 *p)
-{
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1)
@@ -42,20 +34,38 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Eight nibbles of one 32-bit word -> four half2 of exact signed values, as the pairs
-// {k0,k4}, {k1,k5}, {k2,k6}, {k3,k7}. `x` must already be XORed with 0x88888888 so that each
-// nibble holds value + 8. (1024 + n) - 1032 and (1024 + 16 n) / 16 - 72 are exact in fp16.
+// (a & b) ^ c in one LOP3.
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t b, uint32_t c)
+{
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(r) : "r"(a), "r"(b), "r"(c)); // 0x6a = (a & b) ^ c
+    return r;
+}
+
+// First mma of a chain: accumulator input is zero.
+__device__ __forceinline__ void mma_16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// Eight two's-complement nibbles of one 32-bit word -> four half2 of exact signed values, as the
+// pairs {k0,k4}, {k1,k5}, {k2,k6}, {k3,k7}. (x & mask) ^ (0x64006400 | sign bits) builds the fp16
+// numbers 1024 + (n ^ 8) = 1032 + value (low nibbles) or 1024 + 16 (n ^ 8) = 1152 + 16 value (high
+// nibbles) in one LOP3 each; one HADD2 / HFMA2 per pair then removes the offset exactly.
 __device__ __forceinline__ void unpack8(uint32_t x, uint32_t (&h)[4])
 {
-    const uint32_t MAGIC = 0x64006400u; // half2(1024, 1024)
     const __half2 k1032 = __half2half2(__ushort_as_half((unsigned short)0x6408));
     const __half2 k16th = __half2half2(__ushort_as_half((unsigned short)0x2C00));  // 1/16
     const __half2 km72 = __half2half2(__ushort_as_half((unsigned short)0xD480));   // -72
-    uint32_t lo0 = (x & 0x000F000Fu) | MAGIC;
-    uint32_t hi0 = (x & 0x00F000F0u) | MAGIC;
+    uint32_t lo0 = and_xor(x, 0x000F000Fu, 0x64086408u);
+    uint32_t hi0 = and_xor(x, 0x00F000F0u, 0x64806480u);
     const uint32_t y = x >> 8;
-    uint32_t lo1 = (y & 0x000F000Fu) | MAGIC;
-    uint32_t hi1 = (y & 0x00F000F0u) | MAGIC;
+    uint32_t lo1 = and_xor(y, 0x000F000Fu, 0x64086408u);
+    uint32_t hi1 = and_xor(y, 0x00F000F0u, 0x64806480u);
     __half2 r0 = __hsub2(*reinterpret_cast<__half2 *>(&lo0), k1032);
     __half2 r1 = __hfma2(*reinterpret_cast<__half2 *>(&hi0), k16th, km72);
     __half2 r2 = __hsub2(*reinterpret_cast<__half2 *>(&lo1), k1032);
@@ -66,112 +76,209 @@ __device__ __forceinline__ void unpack8(uint32_t x, uint32_t (&h)[4])
     h[3] = *reinterpret_cast<uint32_t *>(&r3);
 }
 
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
-int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act, const uint8_t *__restrict__ w,
-                 const __half *__restrict__ scales, __half *__restrict__ out)
+// Bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned) global -> shared memory of this
+// CTA, completion counted on `bar`.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar)
 {
-    extern __shared__ uint4 act_s[]; // [mrows][K/8 + 1] permuted activations, then the reduction buffer
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+constexpr int GEMV_ROW_PAD = 64; // bytes between staged rows beyond K/2, keeps 128-bit shared loads conflict-free
+
+template <bool kStageAct>
+__global__ void __launch_bounds__(GEMV_WARPS * 32, 5)
+int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act, const uint8_t *__restrict__ w,
+                 const __half *__restrict__ scales, __half *__restrict__ out, int *status)
+{
+    // The CTA's whole weight slab (16 rows x K/2 bytes) is requested from HBM at once with bulk async
+    // copies into shared memory: every byte the kernel needs is in flight a few hundred cycles after
+    // the CTA starts, at no register cost. Each warp owns a contiguous quarter of K, split into two
+    // halves with one mbarrier each, and starts computing as soon as its first half has landed.
+    // kStageAct (M <= 2): the activations are additionally staged in shared memory, already permuted
+    // to the slot order of the unpacked weights, which takes 16 byte-permutes and 4 global loads per
+    // 128-k block out of the inner loop. For more rows that copy would not fit beside the weights.
+    // Shared memory: [16][K/2 + GEMV_ROW_PAD] weights | [16][G] fp16 scales | [mrows][K/8 + 1] uint4 staged
+    // activations (kStageAct only).
+    extern __shared__ __align__(128) uint8_t wsm[];
+    __shared__ __align__(8) uint64_t bars[GEMV_WARPS * 2];
+    __shared__ float red[GEMV_WARPS * 16 * 8]; // cross-warp reduction [warp][16 rows][8 m]
+    __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int m0 = blockIdx.y * 8;
     const int mrows = min(8, M - m0);
     const int n0 = blockIdx.x * GEMV_ROWS;
-    const int rowA = min(n0 + g, N - 1), rowB = min(n0 + g + 8, N - 1);
-    const int nkb = K / 128;  // 128-k blocks per row
-    const int G = K / group;  // scales per row
-    const int units = K / 32; // 16-byte units per weight row
-    const uint4 *wA = reinterpret_cast<const uint4 *>(w) + (size_t)rowA * units + t;
-    const uint4 *wB = reinterpret_cast<const uint4 *>(w) + (size_t)rowB * units + t;
-    const __half *sA = scales + (size_t)rowA * G;
-    const __half *sB = scales + (size_t)rowB * G;
+    const int nkb = K / 128;                                // 128-k blocks per row
+    const int bpw = (nkb + GEMV_WARPS - 1) / GEMV_WARPS;    // blocks per warp
+    const int kb_lo = min(warp * bpw, nkb), kb_hi = min(kb_lo + bpw, nkb);
+    const int kb_mid = kb_lo + (kb_hi - kb_lo + 1) / 2;     // first half [kb_lo, kb_mid), second [kb_mid, kb_hi)
+    const int G = K / group;
+    const int row_bytes = K / 2;
+    const int row_pitch = row_bytes + GEMV_ROW_PAD;
+    const uint32_t wsm_u32 = (uint32_t)__cvta_generic_to_shared(wsm);
+    __half *sc_s = reinterpret_cast<__half *>(wsm + GEMV_ROWS * row_pitch);               // [16][G]
+    const int sc_bytes = (GEMV_ROWS * G * 2 + 15) & ~15;
+    uint4 *act_s = reinterpret_cast<uint4 *>(wsm + GEMV_ROWS * row_pitch + sc_bytes);     // [mrows][act_pitch]
+    const int act_pitch = K / 8 + 1; // uint4 per staged activation row (+1 keeps rows on different banks)
 
-    uint4 qa[GEMV_UNROLL], qb[GEMV_UNROLL];
-    float fa[GEMV_UNROLL], fb[GEMV_UNROLL];
-    // First batch of weight loads goes out before the activations are staged.
-#pragma unroll
-    for (int u = 0; u < GEMV_UNROLL; ++u) {
-        const int kb = warp + GEMV_WARPS * u;
-        if (kb < nkb) {
-            qa[u] = ldg_stream(wA + kb * 4);
-            qb[u] = ldg_stream(wB + kb * 4);
-            const int si = (kb * 128) / group;
-            fa[u] = __half2float(__ldg(sA + si));
-            fb[u] = __half2float(__ldg(sB + si));
-        }
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < GEMV_WARPS * 2; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&bars[i])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 
-    // Stage activations: 8 consecutive k -> [k0,k4,k1,k5,k2,k6,k3,k7], one padded row per m.
-    const int row_u4 = K / 8 + 1;
-    for (int i = threadIdx.x; i < mrows * (K / 8); i += blockDim.x) {
-        const int m = i / (K / 8), j = i - m * (K / 8);
-        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(act + (size_t)(m0 + m) * K) + j);
+    // The small operands (scales, and the activations when they are staged) are requested BEFORE the
+    // weight slab: a load issued after 22 MB of queued weight traffic would only come back once most of
+    // that traffic has drained. They land in registers now and are written to shared memory after the
+    // bulk copies have been issued.
+    constexpr int SC_PRE = 4, ACT_PRE = 4; // per-thread prefetch depth; the rest (large K) is fetched afterwards
+    const int sc_total = GEMV_ROWS * G, act_total = kStageAct ? mrows * (K / 8) : 0;
+    __half sc_pre[SC_PRE];
+    uint4 act_pre[ACT_PRE];
+#pragma unroll
+    for (int j = 0; j < SC_PRE; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < sc_total) {
+            const int r = i / G, gi = i - r * G;
+            sc_pre[j] = __ldg(scales + (size_t)min(n0 + r, N - 1) * G + gi);
+        }
+    }
+    if constexpr (kStageAct) {
+#pragma unroll
+        for (int j = 0; j < ACT_PRE; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < act_total) {
+                const int m = i / (K / 8), c = i - m * (K / 8);
+                act_pre[j] = __ldg(reinterpret_cast<const uint4 *>(act + (size_t)(m0 + m) * K) + c);
+            }
+        }
+    }
+    __syncthreads(); // mbarriers initialised
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&bars[warp * 2]);
+    const uint32_t bar1 = bar0 + 8;
+    {
+        const uint32_t bytes0 = (uint32_t)(kb_mid - kb_lo) * 64u, bytes1 = (uint32_t)(kb_hi - kb_mid) * 64u; // per row
+        if (lane == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar0), "r"(bytes0 * 16u) : "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar1), "r"(bytes1 * 16u) : "memory");
+        }
+        __syncwarp();
+        if (lane < GEMV_ROWS) {
+            const int row = min(n0 + lane, N - 1); // rows past N re-read the last row; their outputs are not stored
+            const uint8_t *src = w + (size_t)row * row_bytes;
+            const uint32_t dst = wsm_u32 + (uint32_t)(lane * row_pitch);
+            if (bytes0) bulk_g2s(dst + kb_lo * 64, src + kb_lo * 64, bytes0, bar0);
+            if (bytes1) bulk_g2s(dst + kb_mid * 64, src + kb_mid * 64, bytes1, bar1);
+        }
+    }
+    // 8 consecutive activations -> {k0,k4}, {k1,k5}, {k2,k6}, {k3,k7}: the slot order of the unpacked weights
+    auto permute8 = [](const uint4 &r) {
         uint4 o;
         o.x = __byte_perm(r.x, r.z, 0x5410);
         o.y = __byte_perm(r.x, r.z, 0x7632);
         o.z = __byte_perm(r.y, r.w, 0x5410);
         o.w = __byte_perm(r.y, r.w, 0x7632);
-        act_s[m * row_u4 + j] = o;
+        return o;
+    };
+#pragma unroll
+    for (int j = 0; j < SC_PRE; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < sc_total) sc_s[i] = sc_pre[j];
     }
-    __syncthreads();
-
-    float tot[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool has_b = g < mrows;
-    const uint4 *arow = act_s + (has_b ? g : 0) * row_u4 + t * 4;
-
-    for (int kb0 = warp; kb0 < nkb; kb0 += GEMV_WARPS * GEMV_UNROLL) {
-        uint4 ca[GEMV_UNROLL], cb[GEMV_UNROLL];
-        float sa[GEMV_UNROLL], sb[GEMV_UNROLL];
+    for (int i = threadIdx.x + SC_PRE * blockDim.x; i < sc_total; i += blockDim.x) {
+        const int r = i / G, gi = i - r * G;
+        sc_s[i] = __ldg(scales + (size_t)min(n0 + r, N - 1) * G + gi);
+    }
+    if constexpr (kStageAct) {
 #pragma unroll
-        for (int u = 0; u < GEMV_UNROLL; ++u) {
-            ca[u] = qa[u];
-            cb[u] = qb[u];
-            sa[u] = fa[u];
-            sb[u] = fb[u];
-        }
-        // Prefetch the next batch while this one is consumed.
-#pragma unroll
-        for (int u = 0; u < GEMV_UNROLL; ++u) {
-            const int kb = kb0 + GEMV_WARPS * (GEMV_UNROLL + u);
-            if (kb < nkb) {
-                qa[u] = ldg_stream(wA + kb * 4);
-                qb[u] = ldg_stream(wB + kb * 4);
-                const int si = (kb * 128) / group;
-                fa[u] = __half2float(__ldg(sA + si));
-                fb[u] = __half2float(__ldg(sB + si));
+        for (int j = 0; j < ACT_PRE; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < act_total) {
+                const int m = i / (K / 8), c = i - m * (K / 8);
+                act_s[m * act_pitch + c] = permute8(act_pre[j]);
             }
         }
+        for (int i = threadIdx.x + ACT_PRE * blockDim.x; i < act_total; i += blockDim.x) {
+            const int m = i / (K / 8), c = i - m * (K / 8);
+            act_s[m * act_pitch + c] = permute8(__ldg(reinterpret_cast<const uint4 *>(act + (size_t)(m0 + m) * K) + c));
+        }
+    }
+    __syncthreads(); // scales (and staged activations) visible to all warps
+    const __half *sA = sc_s + g * G;
+    const __half *sB = sc_s + (g + 8) * G;
+    // Unstaged activations come straight from global memory: a few KB that every CTA on the SM reads, so
+    // L1 hits after the first touch. Lane (g,t) supplies activation row g; lanes beyond the last row read
+    // the last valid row (their output columns are never stored).
+    const uint4 *arow = reinterpret_cast<const uint4 *>(act + (size_t)(m0 + min(g, mrows - 1)) * K) + t * 4;
+    const int bpg = group / 128; // 128-k blocks per scale group
+    const uint4 *arow_s = act_s + min(g, mrows - 1) * act_pitch + t * 4;
+    const uint8_t *myA = wsm + g * row_pitch + t * 16;
+    const uint8_t *myB = wsm + (g + 8) * row_pitch + t * 16;
+
+    float tot[4] = {0.f, 0.f, 0.f, 0.f};
+    bool ok = true;
+#pragma unroll 1
+    for (int half = 0; half < 2 && ok; ++half) {
+        const int b0 = half ? kb_mid : kb_lo, b1 = half ? kb_hi : kb_mid;
+        if (b0 >= b1) continue;
+        ok = mbar_wait_warp(half ? bar1 : bar0, 0u, &abort_flag, status, WAIT_EPI_STAGE);
+        if (!ok) break;
+#pragma unroll 2
+        for (int kb = b0; kb < b1; ++kb) {
+            const uint4 qa = *reinterpret_cast<const uint4 *>(myA + kb * 64);
+            const uint4 qb = *reinterpret_cast<const uint4 *>(myB + kb * 64);
+            const uint32_t xa[4] = {qa.x, qa.y, qa.z, qa.w};
+            const uint32_t xb[4] = {qb.x, qb.y, qb.z, qb.w};
+            const int si = bpg == 1 ? kb : kb / bpg;
+            const float sa = __half2float(sA[si]);
+            const float sb = __half2float(sB[si]);
+            uint4 av[4];
 #pragma unroll
-        for (int u = 0; u < GEMV_UNROLL; ++u) {
-            const int kb = kb0 + GEMV_WARPS * u;
-            if (kb >= nkb) break;
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t xa[4] = {ca[u].x, ca[u].y, ca[u].z, ca[u].w};
-            const uint32_t xb[4] = {cb[u].x, cb[u].y, cb[u].z, cb[u].w};
+            for (int wd = 0; wd < 4; ++wd) av[wd] = kStageAct ? arow_s[kb * 16 + wd] : __ldg(arow + kb * 16 + wd);
+            // Two independent accumulator chains halve the mma dependency depth.
+            float c0[4], c1[4];
 #pragma unroll
             for (int wd = 0; wd < 4; ++wd) {
                 uint32_t ha[4], hb[4];
-                unpack8(xa[wd] ^ 0x88888888u, ha);
-                unpack8(xb[wd] ^ 0x88888888u, hb);
-                uint4 bv = make_uint4(0u, 0u, 0u, 0u);
-                if (has_b) bv = arow[kb * 16 + wd];
-                mma_16816(c, ha[0], hb[0], ha[1], hb[1], bv.x, bv.y);
-                mma_16816(c, ha[2], hb[2], ha[3], hb[3], bv.z, bv.w);
+                unpack8(xa[wd], ha);
+                unpack8(xb[wd], hb);
+                // 8 consecutive activations (k0..k7) -> the slot order of the unpacked weights:
+                // {k0,k4}, {k1,k5}, {k2,k6}, {k3,k7}
+                const uint32_t b04 = kStageAct ? av[wd].x : __byte_perm(av[wd].x, av[wd].z, 0x5410);
+                const uint32_t b15 = kStageAct ? av[wd].y : __byte_perm(av[wd].x, av[wd].z, 0x7632);
+                const uint32_t b26 = kStageAct ? av[wd].z : __byte_perm(av[wd].y, av[wd].w, 0x5410);
+                const uint32_t b37 = kStageAct ? av[wd].w : __byte_perm(av[wd].y, av[wd].w, 0x7632);
+                if (wd == 0) {
+                    mma_16816_first(c0, ha[0], hb[0], ha[1], hb[1], b04, b15);
+                    mma_16816_first(c1, ha[2], hb[2], ha[3], hb[3], b26, b37);
+                } else {
+                    mma_16816(c0, ha[0], hb[0], ha[1], hb[1], b04, b15);
+                    mma_16816(c1, ha[2], hb[2], ha[3], hb[3], b26, b37);
+                }
             }
-            tot[0] = fmaf(sa[u], c[0], tot[0]);
-            tot[1] = fmaf(sa[u], c[1], tot[1]);
-            tot[2] = fmaf(sb[u], c[2], tot[2]);
-            tot[3] = fmaf(sb[u], c[3], tot[3]);
+            tot[0] = fmaf(sa, c0[0] + c1[0], tot[0]);
+            tot[1] = fmaf(sa, c0[1] + c1[1], tot[1]);
+            tot[2] = fmaf(sb, c0[2] + c1[2], tot[2]);
+            tot[3] = fmaf(sb, c0[3] + c1[3], tot[3]);
         }
     }
 
-    // Cross-warp reduction through shared memory (reuses the activation buffer).
-    __syncthreads();
-    float *red = reinterpret_cast<float *>(act_s); // [warp][16 rows][8 m]
+    // Cross-warp reduction through shared memory.
     red[(warp * 16 + g) * 8 + 2 * t] = tot[0];
     red[(warp * 16 + g) * 8 + 2 * t + 1] = tot[1];
     red[(warp * 16 + g + 8) * 8 + 2 * t] = tot[2];
     red[(warp * 16 + g + 8) * 8 + 2 * t + 1] = tot[3];
     __syncthreads();
+    if (abort_flag) {
+        // A wait ran out: give copies still in flight a bounded time to land before the CTA's shared
+        // memory is released, and store nothing.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+        return;
+    }
     {
         const int m = threadIdx.x >> 4, r = threadIdx.x & 15; // 8 m x 16 rows = 128 threads
         float s = 0.f;
@@ -260,12 +367,12 @@ static int grid_for(long long items, int block, int sm_cap)
 }
 
 int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
-                     const void *scales, void *out)
+                     const void *scales, void *out, int *status)
 {
     (void)sm_count;
     if (M == 0 || N == 0) return BTM_OK;
     const bool fast = (K % 128 == 0) && (group % 128 == 0) && (((uintptr_t)act & 15) == 0) && (((uintptr_t)w & 15) == 0) &&
-                      (((uintptr_t)scales & 1) == 0) && K > 0;
+                      (((uintptr_t)scales & 1) == 0) && K > 0 && (size_t)GEMV_ROWS * (K / 2 + GEMV_ROW_PAD + 2 * (K / group)) + 2 * (size_t)(K / 8 + 1) * 16 <= 200 * 1024;
     if (!fast) {
         const long long total = (long long)M * N;
         const int block = 128;
@@ -275,19 +382,22 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
                                                                      (const __half *)scales, (__half *)out);
         return check_cuda(cudaGetLastError(), "int4 general launch");
     }
-    const int mrows = M < 8 ? M : 8;
-    size_t smem = (size_t)mrows * (K / 8 + 1) * sizeof(uint4);
-    const size_t red = GEMV_WARPS * 16 * 8 * sizeof(float);
-    if (smem < red) smem = red;
-    if (smem > 200 * 1024) return set_error(BTM_ERR_UNSUPPORTED, "int4 matmul: K=%d too large for the activation stage", K);
+    dim3 grid((unsigned)((N + GEMV_ROWS - 1) / GEMV_ROWS), (unsigned)((M + 7) / 8));
+    const bool stage_act = M <= 2;
+    size_t smem = (size_t)GEMV_ROWS * (K / 2 + GEMV_ROW_PAD) + (((size_t)GEMV_ROWS * (K / group) * 2 + 15) & ~(size_t)15);
+    if (stage_act) smem += (size_t)M * (K / 8 + 1) * sizeof(uint4);
     if (smem > 48 * 1024) {
-        int rc = check_cuda(cudaFuncSetAttribute(int4_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024),
-                            "cudaFuncSetAttribute(int4_gemv)");
+        cudaError_t e = stage_act ? cudaFuncSetAttribute(int4_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)
+                                  : cudaFuncSetAttribute(int4_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        int rc = check_cuda(e, "cudaFuncSetAttribute(int4_gemv)");
         if (rc) return rc;
     }
-    dim3 grid((unsigned)((N + GEMV_ROWS - 1) / GEMV_ROWS), (unsigned)((M + 7) / 8));
-    int4_gemv_kernel<<<grid, GEMV_WARPS * 32, smem, st>>>(M, N, K, group, (const __half *)act, (const uint8_t *)w,
-                                                          (const __half *)scales, (__half *)out);
+    if (stage_act)
+        int4_gemv_kernel<true><<<grid, GEMV_WARPS * 32, smem, st>>>(M, N, K, group, (const __half *)act, (const uint8_t *)w,
+                                                                    (const __half *)scales, (__half *)out, status);
+    else
+        int4_gemv_kernel<false><<<grid, GEMV_WARPS * 32, smem, st>>>(M, N, K, group, (const __half *)act, (const uint8_t *)w,
+                                                                     (const __half *)scales, (__half *)out, status);
     return check_cuda(cudaGetLastError(), "int4 gemv launch");
 }
 
