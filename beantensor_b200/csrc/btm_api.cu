@@ -105,6 +105,22 @@ int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, u
     return BTM_OK;
 }
 
+int encode_store_maps(StoreMaps *cm, int dtype, const GemmParams &p)
+{
+    memset(cm, 0, sizeof(*cm));
+    if (!p.c_vec_ok) return BTM_OK;
+    const uint64_t es = dtype == BTM_F32 ? 4 : 2;
+    const uint32_t box_cols = dtype == BTM_F32 ? 32 : 64; // 128 bytes per staged row
+    const uint64_t width = (uint64_t)p.col0 + (uint64_t)p.N; // stores are clipped at the last column this launch owns
+    const uint64_t s1 = (uint64_t)p.ldc * es;
+    const uint64_t s2 = p.batch > 1 ? (uint64_t)p.strideC * es : s1;
+    for (int d = 0; d < p.ndst; ++d) {
+        int rc = encode_tmap_3d(&cm->m[d], dtype, p.C[d], width, (uint64_t)p.M, (uint64_t)p.batch, s1, s2, box_cols, 32);
+        if (rc) return rc;
+    }
+    return BTM_OK;
+}
+
 static size_t es_of(int dtype) { return dtype == BTM_F32 ? 4 : 2; }
 static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
@@ -173,8 +189,11 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
         if (!strcmp(force, "1cta")) pair = false;
         else if (!strcmp(force, "2cta")) pair = true;
     }
-    if (pair) return launch_gemm_tc2(c.dtype, st, ds->sm_count, tmA, tmB, p);
-    return launch_gemm_tc(c.dtype, st, ds->sm_count, tmA, tmB, p, 0);
+    StoreMaps cm;
+    rc = encode_store_maps(&cm, c.dtype, p);
+    if (rc) return rc;
+    if (pair) return launch_gemm_tc2(c.dtype, st, ds->sm_count, tmA, tmB, cm, p);
+    return launch_gemm_tc(c.dtype, st, ds->sm_count, tmA, tmB, cm, p, 0);
 }
 
 static int run_f32(DeviceState *ds, cudaStream_t st, const GemmCall &c, void *ws, size_t ws_bytes)
@@ -212,7 +231,10 @@ static int run_f32(DeviceState *ds, cudaStream_t st, const GemmCall &c, void *ws
     p.ldc = c.ldc;
     p.c_vec_ok = (aligned16(c.C[0]) && (c.ldc * 4) % 16 == 0) ? 1 : 0;
     p.status = ds->status;
-    return launch_gemm_tc(BTM_F32, st, ds->sm_count, tmA, tmB, p, bn);
+    StoreMaps cm;
+    rc = encode_store_maps(&cm, BTM_F32, p);
+    if (rc) return rc;
+    return launch_gemm_tc(BTM_F32, st, ds->sm_count, tmA, tmB, cm, p, bn);
 }
 
 static int check_gemm_args(int dtype, int M, int N, int K, const void *A, long long lda, const void *B, long long ldb,
@@ -380,7 +402,10 @@ int btm_gemm_bt(int device, void *stream, int dtype, int M, int N, int K, const 
     p.C[0] = C; p.ldc = ldc;
     p.c_vec_ok = (aligned16(C) && (ldc * (long long)es) % 16 == 0) ? 1 : 0;
     p.status = ds->status;
-    return launch_gemm_tc_bt(dtype, st, ds->sm_count, tmA, tmB, p, bn);
+    StoreMaps cm;
+    rc = encode_store_maps(&cm, dtype, p);
+    if (rc) return rc;
+    return launch_gemm_tc_bt(dtype, st, ds->sm_count, tmA, tmB, cm, p, bn);
 }
 
 int btm_gemm_nshard(int device, void *stream, int dtype, int M, int Nloc, int K, const void *A, int64_t lda,

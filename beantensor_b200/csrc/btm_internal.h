@@ -28,6 +28,11 @@ struct GemmParams {
     int *status;       // device status word (bounded waits report here)
 };
 
+// Output tensor maps of the epilogue's TMA stores, one per destination copy of C (local first, then peers).
+struct StoreMaps {
+    CUtensorMap m[kMaxDst];
+};
+
 // Per-device state, created once by btm_init.
 struct DeviceState {
     bool ready;
@@ -46,9 +51,9 @@ int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, u
                    uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1);
 
 // Launchers (defined next to their kernels). All return a btm_status.
-int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB,
+int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
                    const GemmParams &p, int force_bn);
-int launch_gemm_tc_bt(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB,
+int launch_gemm_tc_bt(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
                       const GemmParams &p, int bn);
 int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K, const void *A, long long lda,
                      long long strideA, const void *B, long long ldb, long long strideB, void *C, long long ldc,
@@ -63,6 +68,9 @@ int launch_int4_dequant(cudaStream_t st, int N, int K, int group, const void *w,
 int launch_int4_unpack(cudaStream_t st, int N, int K, const void *w, void *out);
 int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once per device
 int configure_gemm_tc2_kernels();
-int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p);
+int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
+                    const GemmParams &p);
+// Fills `cm` for the destinations in `p` (no-op when p.c_vec_ok == 0: the general store path needs no maps).
+int encode_store_maps(StoreMaps *cm, int dtype, const GemmParams &p);
 
 } // namespace btm

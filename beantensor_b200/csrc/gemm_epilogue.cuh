@@ -1,0 +1,161 @@
+// Epilogue of the tensor-core matmul kernels: accumulator (tensor memory) -> output type -> C.
+//
+// Fast path (C base, pitch and column offset 16-byte aligned): every epilogue warp owns a 32-row
+// band of the tile. It reads 32 accumulator columns at a time with tcgen05.ld, rounds to the output
+// type and writes them into a warp-private shared-memory tile of 32 rows x 128 bytes laid out with
+// the 128-byte swizzle (conflict-free 16-byte stores); one lane then hands the tile to a TMA store
+// (cp.async.bulk.tensor ... global.shared::cta), once per destination copy of C. The TMA unit clips
+// rows and columns beyond the matrix, so the band needs no predicates, and C is written in whole
+// 128-byte lines. Two tiles per warp alternate so that a store drains while the next is filled.
+// General path (unaligned C): per-thread row stores, as the kernels did originally.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "btm_internal.h"
+#include "btm_ptx.cuh"
+
+namespace btm {
+
+constexpr int EPI_TILE_BYTES = 32 * 128;           // one staging tile: 32 rows x 128 B
+constexpr int EPI_WARP_BYTES = 2 * EPI_TILE_BYTES; // two tiles per epilogue warp
+constexpr int EPI_SMEM_BYTES = 4 * EPI_WARP_BYTES; // four epilogue warps
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *m, uint32_t src_smem, int x, int y, int z)
+{
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(m), "r"(src_smem), "r"(x),
+                 "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's bulk groups still have to READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+template <int DT>
+__device__ __forceinline__ void pack16(const uint32_t (&acc)[32], uint32_t (&packed)[16])
+{
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float lo = __uint_as_float(acc[2 * j]), hi = __uint_as_float(acc[2 * j + 1]);
+        if constexpr (DT == BTM_F16) {
+            __half2 h = __floats2half2_rn(lo, hi);
+            packed[j] = *reinterpret_cast<uint32_t *>(&h);
+        } else {
+            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+            packed[j] = *reinterpret_cast<uint32_t *>(&h);
+        }
+    }
+}
+
+// Per-thread stores of 32 consecutive columns of one output row (general path).
+template <int DT>
+__device__ __forceinline__ void store_row_direct(const GemmParams &p, const uint32_t (&acc)[32], long long elem_off, int ncols_valid)
+{
+    if constexpr (DT == BTM_F32) {
+        for (int d = 0; d < p.ndst; ++d) {
+            float *dst = reinterpret_cast<float *>(p.C[d]) + elem_off;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols_valid) dst[j] = __uint_as_float(acc[j]);
+        }
+    } else {
+        uint32_t packed[16];
+        pack16<DT>(acc, packed);
+        for (int d = 0; d < p.ndst; ++d) {
+            uint16_t *dst = reinterpret_cast<uint16_t *>(p.C[d]) + elem_off;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols_valid) dst[j] = (uint16_t)((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xFFFFu));
+        }
+    }
+}
+
+// Drains one 32-row band (this warp's tensor-memory quadrant) of a finished tile.
+//   tmem_band   tensor-memory address of the band's first accumulator column (lane bits included)
+//   row0        first output row of the band; col_first first output column of the tile; bn its width
+//   epi_smem    this warp's two staging tiles (shared-memory address, 1024-byte aligned)
+//   tile_count  running count of staging tiles this warp has used (selects the buffer)
+template <int DT>
+__device__ __forceinline__ void epilogue_band(const GemmParams &p, const StoreMaps &cmaps, uint32_t tmem_band, int row0, int col_first,
+                                              int bn, int batch, uint32_t epi_smem, uint32_t &tile_count, int lane)
+{
+    constexpr int kColsPerTile = (DT == BTM_F32) ? 32 : 64; // 128 bytes of output per row
+    if (!p.c_vec_ok) {
+        const int row = row0 + lane;
+        const long long row_off = (long long)batch * p.strideC + (long long)row * p.ldc + p.col0;
+#pragma unroll 1
+        for (int c = 0; c < bn / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_band + (uint32_t)(c * 32), v);
+            tmem_ld_wait();
+            const int col = col_first + c * 32;
+            const int valid = min(32, p.N - col);
+            if (row < p.M && valid > 0) store_row_direct<DT>(p, v, row_off + col, valid);
+        }
+        return;
+    }
+    const uint32_t swz = (uint32_t)(lane & 7);
+#pragma unroll 1
+    for (int c = 0; c < bn / kColsPerTile; ++c) {
+        const uint32_t buf = epi_smem + (tile_count & 1u) * EPI_TILE_BYTES;
+        ++tile_count;
+        // The store issued two tiles ago used this buffer: it must have finished reading it.
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        const uint32_t row_addr = buf + (uint32_t)lane * 128u;
+        if constexpr (DT == BTM_F32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_band + (uint32_t)(c * 32), v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) st_shared_v4(row_addr + (((uint32_t)j ^ swz) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t v[32], q[16];
+                tmem_ld_32x32(tmem_band + (uint32_t)(c * 64 + h * 32), v);
+                tmem_ld_wait();
+                pack16<DT>(v, q);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    st_shared_v4(row_addr + (((uint32_t)(h * 4 + j) ^ swz) << 4), q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
+            }
+        }
+        fence_proxy_async_smem(); // generic-proxy writes above -> visible to the TMA unit
+        __syncwarp();
+        const int col = col_first + c * kColsPerTile;
+        if (lane == 0) {
+            if (row0 < p.M && col < p.N) {
+                const int x = (int)p.col0 + col;
+#pragma unroll
+                for (int d = 0; d < kMaxDst; ++d) {
+                    if (d >= p.ndst) break;
+                    tma_store_3d(&cmaps.m[d], buf, x, row0, batch);
+                }
+            }
+            bulk_commit(); // an empty group when nothing was stored keeps the buffer accounting uniform
+        }
+    }
+}
+
+// Before the warp leaves the kernel: every store it issued has completed.
+__device__ __forceinline__ void epilogue_drain(int lane)
+{
+    if (lane == 0) bulk_wait_all<0>();
+    __syncwarp();
+}
+
+} // namespace btm

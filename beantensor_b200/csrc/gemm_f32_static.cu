@@ -169,7 +169,9 @@ extern "C" int btm_gemm_f32_static(int device, void *stream, int M, int N, int K
     p.ndst = 1;
     p.C[0] = C;
     p.ldc = ldc;
-    p.c_vec_ok = ((((uintptr_t)C) & 15) == 0 && (ldc * 4) % 16 == 0) ? 1 : 0;
+    p.c_vec_ok = 0; // per-thread row stores: this variant encodes no output tensor map
     p.status = s->status;
-    return launch_gemm_tc(BTM_F32, st, s->sm_count, tmA, tmB, p, bn);
+    StoreMaps cm;
+    memset(&cm, 0, sizeof(cm));
+    return launch_gemm_tc(BTM_F32, st, s->sm_count, tmA, tmB, cm, p, bn);
 }

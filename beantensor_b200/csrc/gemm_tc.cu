@@ -19,6 +19,7 @@
 
 #include "btm_internal.h"
 #include "btm_ptx.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace btm {
 
@@ -44,7 +45,7 @@ struct TileCfg {
     static constexpr int kBBytes = BN * SLICE_BYTES;        // one B plane (either major)
     static constexpr int kStageBytes = kPlanes * (kABytes + kBBytes);
     static constexpr int kStages = (kStageBytes <= 48 * 1024) ? 4 : 3;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024; // + alignment slack
+    static constexpr int kSmemBytes = kStages * kStageBytes + EPI_SMEM_BYTES + 1024; // ring + epilogue staging + alignment slack
     static constexpr int kTmemCols = 2 * BN;                // two accumulators
     static constexpr int kKSteps = SLICE_BYTES / UMMA_K_BYTES;
     static constexpr int kUmmaKRows = UMMA_K_BYTES / kEs;   // k rows of B per mma
@@ -81,65 +82,10 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int tile_i
     return c;
 }
 
-template <int DT>
-__device__ __forceinline__ void store_row_chunk(const GemmParams &p, const uint32_t (&acc)[32], long long elem_off,
-                                                int ncols_valid)
-{
-    // acc holds 32 consecutive fp32 columns of one output row; elem_off is the element offset
-    // of the first of them inside C. ncols_valid <= 32 trims the right edge of the matrix.
-    if constexpr (DT == BTM_F32) {
-        if (ncols_valid == 32 && p.c_vec_ok) {
-#pragma unroll
-            for (int d = 0; d < kMaxDst; ++d) {
-                if (d >= p.ndst) break;
-                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<float *>(p.C[d]) + elem_off);
-#pragma unroll
-                for (int v = 0; v < 8; ++v) dst[v] = make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
-            }
-        } else {
-            for (int d = 0; d < p.ndst; ++d) {
-                float *dst = reinterpret_cast<float *>(p.C[d]) + elem_off;
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (j < ncols_valid) dst[j] = __uint_as_float(acc[j]);
-            }
-        }
-    } else {
-        uint32_t packed[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float lo = __uint_as_float(acc[2 * j]), hi = __uint_as_float(acc[2 * j + 1]);
-            if constexpr (DT == BTM_F16) {
-                __half2 h = __floats2half2_rn(lo, hi);
-                packed[j] = *reinterpret_cast<uint32_t *>(&h);
-            } else {
-                __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                packed[j] = *reinterpret_cast<uint32_t *>(&h);
-            }
-        }
-        if (ncols_valid == 32 && p.c_vec_ok) {
-#pragma unroll
-            for (int d = 0; d < kMaxDst; ++d) {
-                if (d >= p.ndst) break;
-                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(p.C[d]) + elem_off);
-#pragma unroll
-                for (int v = 0; v < 4; ++v)
-                    dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-            }
-        } else {
-            for (int d = 0; d < p.ndst; ++d) {
-                uint16_t *dst = reinterpret_cast<uint16_t *>(p.C[d]) + elem_off;
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (j < ncols_valid) dst[j] = (uint16_t)((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xFFFFu));
-            }
-        }
-    }
-}
-
 template <int BN, int DT, bool BT = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ StoreMaps cmaps, const GemmParams p)
 {
     using Cfg = TileCfg<BN, DT, BT>;
     extern __shared__ uint8_t smem_raw[];
@@ -274,6 +220,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int quad = warp & 3; // tensor-memory lane quadrant this warp may read
+        const uint32_t epi_smem = smem_base + Cfg::kStages * Cfg::kStageBytes + (uint32_t)quad * EPI_WARP_BYTES;
+        uint32_t epi_tiles = 0;
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
             const TileCoord tc = decode_tile<BN>(p, tile);
@@ -282,21 +230,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // One lane waits and broadcasts the verdict: tcgen05.ld below needs the whole warp.
             if (!mbar_wait_warp(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL)) break;
             tc_fence_after();
-            const int row = tc.m * BM + quad * 32 + lane;
-            const long long row_off = (long long)tc.b * p.strideC + (long long)row * p.ldc + p.col0;
-#pragma unroll 1
-            for (int c = 0; c < tc.bn / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
-                tmem_ld_wait();
-                const int col = tc.n0 + c * 32;
-                const int valid = min(32, p.N - col);
-                if (row < p.M && valid > 0) store_row_chunk<DT>(p, v, row_off + col, valid);
-            }
+            epilogue_band<DT>(p, cmaps, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN), tc.m * BM + quad * 32, tc.n0,
+                              tc.bn, tc.b, epi_smem, epi_tiles, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
         }
+        epilogue_drain(lane);
     }
 
     // ---------------------------------------------------------------- teardown
@@ -378,7 +318,7 @@ int launch_split_tf32(cudaStream_t st, const float *src, long long ld, int rows,
 }
 
 template <int BN, int DT, bool BT = false>
-static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, GemmParams p)
+static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm, GemmParams p)
 {
     using Cfg = TileCfg<BN, DT, BT>;
     p.tiles_m = (p.M + BM - 1) / BM;
@@ -397,7 +337,7 @@ static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, con
     p.tiles_tail = 2 * tail_big;
     const long long sched = (long long)p.tiles_full + p.tiles_tail;
     const int grid = (int)(sched < sm_count ? sched : sm_count);
-    gemm_tc_kernel<BN, DT, BT><<<grid, NUM_THREADS, Cfg::kSmemBytes, st>>>(tmA, tmB, p);
+    gemm_tc_kernel<BN, DT, BT><<<grid, NUM_THREADS, Cfg::kSmemBytes, st>>>(tmA, tmB, cm, p);
     return check_cuda(cudaGetLastError(), "gemm_tc launch");
 }
 
@@ -424,7 +364,7 @@ int configure_gemm_tc_kernels()
     return check_cuda(e, "cudaFuncSetAttribute(gemm_tc)");
 }
 
-int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB,
+int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
                    const GemmParams &p, int force_bn)
 {
     // Tile width: 256 columns unless the output is so small that narrower tiles are needed to
@@ -435,8 +375,8 @@ int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &
             const long long t128 = (long long)p.batch * ((p.M + BM - 1) / BM) * ((p.N + 127) / 128);
             if (t128 < sm_count) bn = 64;
         }
-        if (bn == 64) return launch_one<64, BTM_F32>(st, sm_count, tmA, tmB, p);
-        return launch_one<128, BTM_F32>(st, sm_count, tmA, tmB, p);
+        if (bn == 64) return launch_one<64, BTM_F32>(st, sm_count, tmA, tmB, cm, p);
+        return launch_one<128, BTM_F32>(st, sm_count, tmA, tmB, cm, p);
     }
     int bn = force_bn ? force_bn : 256;
     if (!force_bn) {
@@ -444,24 +384,24 @@ int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &
         if (t256 < sm_count) bn = 128;
     }
     if (dtype == BTM_F16) {
-        if (bn == 128) return launch_one<128, BTM_F16>(st, sm_count, tmA, tmB, p);
-        return launch_one<256, BTM_F16>(st, sm_count, tmA, tmB, p);
+        if (bn == 128) return launch_one<128, BTM_F16>(st, sm_count, tmA, tmB, cm, p);
+        return launch_one<256, BTM_F16>(st, sm_count, tmA, tmB, cm, p);
     }
-    if (bn == 128) return launch_one<128, BTM_BF16>(st, sm_count, tmA, tmB, p);
-    return launch_one<256, BTM_BF16>(st, sm_count, tmA, tmB, p);
+    if (bn == 128) return launch_one<128, BTM_BF16>(st, sm_count, tmA, tmB, cm, p);
+    return launch_one<256, BTM_BF16>(st, sm_count, tmA, tmB, cm, p);
 }
 
 // 16-bit product with B given transposed ([N,K] row-major, i.e. K-major): C = A . Bt^T. The B box of
 // the tensor map is one whole tile (bn rows x 64 k), so the caller fixes bn (256 or 128).
-int launch_gemm_tc_bt(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB,
+int launch_gemm_tc_bt(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
                       const GemmParams &p, int bn)
 {
     if (dtype == BTM_F16) {
-        if (bn == 128) return launch_one<128, BTM_F16, true>(st, sm_count, tmA, tmB, p);
-        return launch_one<256, BTM_F16, true>(st, sm_count, tmA, tmB, p);
+        if (bn == 128) return launch_one<128, BTM_F16, true>(st, sm_count, tmA, tmB, cm, p);
+        return launch_one<256, BTM_F16, true>(st, sm_count, tmA, tmB, cm, p);
     }
-    if (bn == 128) return launch_one<128, BTM_BF16, true>(st, sm_count, tmA, tmB, p);
-    return launch_one<256, BTM_BF16, true>(st, sm_count, tmA, tmB, p);
+    if (bn == 128) return launch_one<128, BTM_BF16, true>(st, sm_count, tmA, tmB, cm, p);
+    return launch_one<256, BTM_BF16, true>(st, sm_count, tmA, tmB, cm, p);
 }
 
 } // namespace btm

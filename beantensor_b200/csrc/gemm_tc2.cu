@@ -22,6 +22,7 @@
 
 #include "btm_internal.h"
 #include "btm_ptx.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace btm {
 
@@ -37,7 +38,7 @@ constexpr int STAGE_BYTES = A_BYTES + 2 * CHUNK_BYTES; // 16 KB + 16 KB
 #define BTM_TC2_STAGES 6
 #endif
 constexpr int STAGES = BTM_TC2_STAGES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_SMEM_BYTES + 1024; // ring + epilogue staging + alignment slack
 constexpr int TMEM_COLS = 512;    // two 256-column accumulators
 constexpr int THREADS = 192;
 } // namespace tc2
@@ -88,41 +89,9 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
 }
 
 template <int DT>
-__device__ __forceinline__ void store_chunk16(const GemmParams &p, const uint32_t (&acc)[32], long long elem_off, int ncols_valid)
-{
-    uint32_t packed[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const float lo = __uint_as_float(acc[2 * j]), hi = __uint_as_float(acc[2 * j + 1]);
-        if constexpr (DT == BTM_F16) {
-            __half2 h = __floats2half2_rn(lo, hi);
-            packed[j] = *reinterpret_cast<uint32_t *>(&h);
-        } else {
-            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-            packed[j] = *reinterpret_cast<uint32_t *>(&h);
-        }
-    }
-    if (ncols_valid == 32 && p.c_vec_ok) {
-#pragma unroll
-        for (int d = 0; d < kMaxDst; ++d) {
-            if (d >= p.ndst) break;
-            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(p.C[d]) + elem_off);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-        }
-    } else {
-        for (int d = 0; d < p.ndst; ++d) {
-            uint16_t *dst = reinterpret_cast<uint16_t *>(p.C[d]) + elem_off;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (j < ncols_valid) dst[j] = (uint16_t)((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xFFFFu));
-        }
-    }
-}
-
-template <int DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc2::THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ StoreMaps cmaps, const GemmParams p)
 {
     using namespace tc2;
     extern __shared__ uint8_t smem_raw[];
@@ -239,25 +208,18 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
         const int quad = warp & 3;
+        const uint32_t epi_smem = smem_base + STAGES * STAGE_BYTES + (uint32_t)quad * EPI_WARP_BYTES;
+        uint32_t epi_tiles = 0;
         int it = 0;
         for (int tile = cluster_id; tile < total_tiles; tile += num_clusters, ++it) {
             const PairTile pt = decode_pair_tile(p, tile);
             const int acc = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            // One lane waits and broadcasts the verdict: tcgen05.ld below needs the whole warp.
             if (!mbar_wait_warp<true>(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL)) break;
             tc_fence_after();
-            const int row = pt.m * PAIR_M + (int)rank * CTA_M + quad * 32 + lane;
-            const long long row_off = (long long)pt.b * p.strideC + (long long)row * p.ldc + p.col0;
-            const int nchunks = pt.bn >> 5;
-#pragma unroll 1
-            for (int c = 0; c < nchunks; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
-                tmem_ld_wait();
-                const int col = pt.n0 + c * 32;
-                const int valid = min(32, p.N - col);
-                if (row < p.M && valid > 0) store_chunk16<DT>(p, v, row_off + col, valid);
-            }
+            epilogue_band<DT>(p, cmaps, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN),
+                              pt.m * PAIR_M + (int)rank * CTA_M + quad * 32, pt.n0, pt.bn, pt.b, epi_smem, epi_tiles, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -265,6 +227,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 else mbar_arrive_cluster(smem_u32(&bar_tmem_empty[acc]), 0);
             }
         }
+        epilogue_drain(lane);
     }
 
     // ---------------------------------------------------------------- teardown
@@ -284,7 +247,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 template <int DT>
-static int launch_pair(cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, GemmParams p)
+static int launch_pair(cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm, GemmParams p)
 {
     using namespace tc2;
     p.tiles_m = (p.M + PAIR_M - 1) / PAIR_M;
@@ -326,7 +289,7 @@ static int launch_pair(cudaStream_t st, int sm_count, const CUtensorMap &tmA, co
     p.tiles_tail = 2 * tail_big;
     const long long sched = (long long)p.tiles_full + p.tiles_tail;
     const int clusters = (int)(sched < max_clusters ? sched : max_clusters);
-    gemm_tc2_kernel<DT><<<2 * clusters, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
+    gemm_tc2_kernel<DT><<<2 * clusters, THREADS, SMEM_BYTES, st>>>(tmA, tmB, cm, p);
     return check_cuda(cudaGetLastError(), "gemm_tc2 launch");
 }
 
@@ -337,10 +300,11 @@ int configure_gemm_tc2_kernels()
     return check_cuda(e, "cudaFuncSetAttribute(gemm_tc2)");
 }
 
-int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p)
+int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
+                    const GemmParams &p)
 {
-    if (dtype == BTM_F16) return launch_pair<BTM_F16>(st, sm_count, tmA, tmB, p);
-    if (dtype == BTM_BF16) return launch_pair<BTM_BF16>(st, sm_count, tmA, tmB, p);
+    if (dtype == BTM_F16) return launch_pair<BTM_F16>(st, sm_count, tmA, tmB, cm, p);
+    if (dtype == BTM_BF16) return launch_pair<BTM_BF16>(st, sm_count, tmA, tmB, cm, p);
     return set_error(BTM_ERR_UNSUPPORTED, "two-SM matmul: dtype %d is not supported", dtype);
 }
 

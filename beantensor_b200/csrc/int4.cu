@@ -141,19 +141,16 @@ int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act,
 #pragma unroll
     for (int j = 0; j < SC_PRE; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
-        if (i < sc_total) {
-            const int r = i / G, gi = i - r * G;
-            sc_pre[j] = __ldg(scales + (size_t)min(n0 + r, N - 1) * G + gi);
-        }
+        // The 16 rows' scales are one contiguous span of [N,G]; past the last row the index is clamped
+        // (those rows are never stored).
+        if (i < sc_total) sc_pre[j] = __ldg(scales + min((size_t)n0 * G + i, (size_t)N * G - 1));
     }
     if constexpr (kStageAct) {
 #pragma unroll
         for (int j = 0; j < ACT_PRE; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
-            if (i < act_total) {
-                const int m = i / (K / 8), c = i - m * (K / 8);
-                act_pre[j] = __ldg(reinterpret_cast<const uint4 *>(act + (size_t)(m0 + m) * K) + c);
-            }
+            // rows m0.. of act are contiguous: uint4 index i of the span
+            if (i < act_total) act_pre[j] = __ldg(reinterpret_cast<const uint4 *>(act + (size_t)m0 * K) + i);
         }
     }
     __syncthreads(); // mbarriers initialised
@@ -188,23 +185,17 @@ int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act,
         const int i = threadIdx.x + j * blockDim.x;
         if (i < sc_total) sc_s[i] = sc_pre[j];
     }
-    for (int i = threadIdx.x + SC_PRE * blockDim.x; i < sc_total; i += blockDim.x) {
-        const int r = i / G, gi = i - r * G;
-        sc_s[i] = __ldg(scales + (size_t)min(n0 + r, N - 1) * G + gi);
-    }
+    for (int i = threadIdx.x + SC_PRE * blockDim.x; i < sc_total; i += blockDim.x)
+        sc_s[i] = __ldg(scales + min((size_t)n0 * G + i, (size_t)N * G - 1));
     if constexpr (kStageAct) {
 #pragma unroll
         for (int j = 0; j < ACT_PRE; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
-            if (i < act_total) {
-                const int m = i / (K / 8), c = i - m * (K / 8);
-                act_s[m * act_pitch + c] = permute8(act_pre[j]);
-            }
+            // at most two staged rows: the row index is a compare, not a division
+            if (i < act_total) act_s[i + (i >= K / 8 ? 1 : 0)] = permute8(act_pre[j]);
         }
-        for (int i = threadIdx.x + ACT_PRE * blockDim.x; i < act_total; i += blockDim.x) {
-            const int m = i / (K / 8), c = i - m * (K / 8);
-            act_s[m * act_pitch + c] = permute8(__ldg(reinterpret_cast<const uint4 *>(act + (size_t)(m0 + m) * K) + c));
-        }
+        for (int i = threadIdx.x + ACT_PRE * blockDim.x; i < act_total; i += blockDim.x)
+            act_s[i + (i >= K / 8 ? 1 : 0)] = permute8(__ldg(reinterpret_cast<const uint4 *>(act + (size_t)m0 * K) + i));
     }
     __syncthreads(); // scales (and staged activations) visible to all warps
     const __half *sA = sc_s + g * G;
@@ -226,13 +217,13 @@ int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act,
         if (b0 >= b1) continue;
         ok = mbar_wait_warp(half ? bar1 : bar0, 0u, &abort_flag, status, WAIT_EPI_STAGE);
         if (!ok) break;
-#pragma unroll 2
+#pragma unroll 4
         for (int kb = b0; kb < b1; ++kb) {
             const uint4 qa = *reinterpret_cast<const uint4 *>(myA + kb * 64);
             const uint4 qb = *reinterpret_cast<const uint4 *>(myB + kb * 64);
             const uint32_t xa[4] = {qa.x, qa.y, qa.z, qa.w};
             const uint32_t xb[4] = {qb.x, qb.y, qb.z, qb.w};
-            const int si = bpg == 1 ? kb : kb / bpg;
+            const int si = bpg == 1 ? kb : (int)((unsigned)kb / (unsigned)bpg);
             const float sa = __half2float(sA[si]);
             const float sb = __half2float(sB[si]);
             uint4 av[4];

@@ -147,6 +147,33 @@ def time_region(torch, dist, world, fn, steps, warmup):
     return ms, t0, t1
 
 
+def time_graph(torch, fn, sets, steps, warmup):
+    """Device time per launch with the host launch path taken out: `fn(i)` for one full rotation of the
+    buffer sets is captured in a CUDA graph and the graph is replayed until `steps` launches have run.
+    Returns microseconds per launch."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(max(warmup, 3)):
+            fn(i)  # also lets the library create its per-device state outside the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(sets):
+                fn(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        replays = max(1, (steps + sets - 1) // sets)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    torch.cuda.current_stream().wait_stream(side)
+    return e0.elapsed_time(e1) / (replays * sets) * 1e3
+
+
 def synth_f16(shape, std, seed, stream, dtype):
     """Seeded normal(0, std) in 16-bit storage; large matrices tile a 4096 x 4096 seeded block."""
     import numpy as np
@@ -269,10 +296,12 @@ def bench_int4(torch, ops, peaks, M, steps, warmup):
         ops.matmul_int4_gpu(a, ws[i % sets], ss[i % sets], out, G)
 
     ms, _, _ = time_region(torch, None, 1, step, steps, warmup)
-    us = ms / steps * 1e3
+    us_host = ms / steps * 1e3  # one Python call per launch: bounded by the host launch path
+    us = time_graph(torch, step, sets, steps, warmup)
     algo = w_bytes + N * (K // G) * 2 + M * K * 2 + M * N * 2
     gbs = algo / (us * 1e-6) / 1e9
     return {"workload": f"int4 weight-only matmul M={M} N=11008 K=4096 group=128", "us_per_launch": us,
+            "us_per_launch_host_loop": us_host, "launch": f"CUDA graph of {sets} launches, replayed",
             "algorithmic_bytes": algo, "value": gbs, "unit": "GB/s",
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs / peaks["hbm_gbs"], "frac_nominal": gbs / NOMINAL_HBM_GBS,
@@ -294,11 +323,13 @@ def bench_bmm(torch, ops, peaks, steps, warmup):
         ops.bmm_gpu(a, b, c)
 
     ms, _, _ = time_region(torch, None, 1, step, steps, warmup)
-    us = ms / steps * 1e3
+    us_host = ms / steps * 1e3
+    us = time_graph(torch, step, sets, steps, warmup)
     algo = (Bn * M * K + Bn * K * N + Bn * M * N) * 2
     gbs = algo / (us * 1e-6) / 1e9
     tf = 2.0 * Bn * M * N * K / (us * 1e-6) / 1e12
-    return {"workload": "batched fp16 matmul [64,512,128]x[64,128,512]", "us_per_launch": us, "algorithmic_bytes": algo,
+    return {"workload": "batched fp16 matmul [64,512,128]x[64,128,512]", "us_per_launch": us, "us_per_launch_host_loop": us_host,
+            "launch": f"CUDA graph of {sets} launches, replayed", "algorithmic_bytes": algo,
             "value": gbs, "unit": "GB/s", "tflops": tf,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs / peaks["hbm_gbs"], "frac_nominal": gbs / NOMINAL_HBM_GBS, "traffic": None},
@@ -313,8 +344,10 @@ def bench_f32(torch, ops, steps, warmup):
     b = torch.from_numpy(synth.uniform((n, n), -1, 1, 0, 1).astype(np.float32)).cuda()
     c = torch.empty((n, n), dtype=torch.float32, device="cuda")
     ms, _, _ = time_region(torch, None, 1, lambda i: ops.matmul_gpu(a, b, c), steps, warmup)
-    us = ms / steps * 1e3
-    return {"workload": "fp32 dense matmul M=N=K=1024 (3xTF32 split)", "us_per_launch": us,
+    us_host = ms / steps * 1e3
+    us = time_graph(torch, lambda i: ops.matmul_gpu(a, b, c), 8, steps, warmup)
+    return {"workload": "fp32 dense matmul M=N=K=1024 (3xTF32 split)", "us_per_launch": us, "us_per_launch_host_loop": us_host,
+            "launch": "CUDA graph of 8 products (3 kernels each), replayed",
             "value": 2.0 * n ** 3 / (us * 1e-6) / 1e12, "unit": "TFLOP/s", "launches_per_step": 3}
 
 
@@ -376,9 +409,13 @@ def run_single(args, peaks):
         "config": {"workload": f"fp16 dense GEMM M=N=K={n}, row-major A[M,K] B[K,N], fp32 accumulate, fp16 out",
                    "l2": f"{sets} rotating A/B/C sets ({sets * 3 * n * n * 2 >> 20} MiB > 126 MiB L2)",
                    "kernel": args.force_kernel or "library choice"},
-        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": tflops / peaks["bf16_tflops"], "frac_nominal": tflops / NOMINAL_TFLOPS,
-                     "peak_source": peaks["_source"] + " cuBLAS bf16 burst", "traffic": NCU_TRAFFIC["gemm_f16_4096"]},
+        # The timed loop runs well past the point where the 1 kW power cap pulls the SM clock down, so the
+        # denominator is the sustained cuBLAS figure; the burst figure is given beside it.
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": tflops / peaks["bf16_tflops_sustained"], "frac_of_burst_peak": tflops / peaks["bf16_tflops"],
+                     "frac_nominal": tflops / NOMINAL_TFLOPS,
+                     "peak_source": peaks["_source"] + " cuBLAS bf16 sustained (timed region >> power-cap onset)",
+                     "traffic": NCU_TRAFFIC["gemm_f16_4096"]},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
         "gpu_launches": args.steps,
