@@ -184,7 +184,9 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
     // part of the machine; single CTAs (128 x 256 or 128 x 128) for small outputs.
     // BTM_FORCE_KERNEL=1cta|2cta overrides the choice (used by the tests to cover both on every shape).
     const long long pair_tiles = (long long)c.batch * ((c.M + 255) / 256) * ((c.N + 255) / 256);
-    bool pair = c.M > 128 && pair_tiles >= ds->sm_count / 4;
+    // Short products (K < 512, e.g. the batched 512x512x128 workload) stay on single CTAs: with two k-blocks
+    // per tile the pair handshake costs more than the halved B traffic saves (12.1 vs 15.7 us measured).
+    bool pair = c.M > 128 && pair_tiles >= ds->sm_count / 4 && c.K >= 512;
     if (const char *force = getenv("BTM_FORCE_KERNEL")) {
         if (!strcmp(force, "1cta")) pair = false;
         else if (!strcmp(force, "2cta")) pair = true;

@@ -279,6 +279,183 @@ int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act,
     }
 }
 
+// Eight nibbles of one word -> four half2 in NATURAL pair order {k0,k1}, {k2,k3}, {k4,k5}, {k6,k7}, so that
+// activations can be used as they lie in memory. A byte-permute puts each byte in both halves of a word;
+// (x & 0x00F0000F) ^ 0x64806408 then makes {1032 + v_even, 1152 + 16 v_odd} and one HFMA2 with per-half
+// constants {1, 1/16} and {-1032, -72} removes the offsets exactly.
+__device__ __forceinline__ void unpack8_natural(uint32_t x, uint32_t (&h)[4])
+{
+    const __half2 mul = __halves2half2(__ushort_as_half((unsigned short)0x3C00), __ushort_as_half((unsigned short)0x2C00)); // {1, 1/16}
+    const __half2 add = __halves2half2(__ushort_as_half((unsigned short)0xE408), __ushort_as_half((unsigned short)0xD480)); // {-1032, -72}
+    const uint32_t y = __byte_perm(x, x, 0x1010); // bytes b0 b1 b0 b1
+    const uint32_t z = __byte_perm(x, x, 0x3232); // bytes b2 b3 b2 b3
+    uint32_t p01 = and_xor(y, 0x00F0000Fu, 0x64806408u);
+    uint32_t p23 = and_xor(y >> 8, 0x00F0000Fu, 0x64806408u);
+    uint32_t p45 = and_xor(z, 0x00F0000Fu, 0x64806408u);
+    uint32_t p67 = and_xor(z >> 8, 0x00F0000Fu, 0x64806408u);
+    __half2 r0 = __hfma2(*reinterpret_cast<__half2 *>(&p01), mul, add);
+    __half2 r1 = __hfma2(*reinterpret_cast<__half2 *>(&p23), mul, add);
+    __half2 r2 = __hfma2(*reinterpret_cast<__half2 *>(&p45), mul, add);
+    __half2 r3 = __hfma2(*reinterpret_cast<__half2 *>(&p67), mul, add);
+    h[0] = *reinterpret_cast<uint32_t *>(&r0);
+    h[1] = *reinterpret_cast<uint32_t *>(&r1);
+    h[2] = *reinterpret_cast<uint32_t *>(&r2);
+    h[3] = *reinterpret_cast<uint32_t *>(&r3);
+}
+
+// int4 matmul for 8 < M <= 64 per launch row-group: the structure of int4_gemv_kernel (weight slab
+// staged once with bulk copies, 16 weight rows per CTA, K split over 4 warps), but every unpacked
+// weight block is reused for MB activation row-blocks of 8, so the weights are read from HBM and
+// unpacked once for up to 64 rows. Activations are read in natural order from global memory (L1/L2).
+template <int MB>
+__global__ void __launch_bounds__(GEMV_WARPS * 32, 4)
+int4_gemm_mma_kernel(int M, int N, int K, int group, const __half *__restrict__ act, const uint8_t *__restrict__ w,
+                     const __half *__restrict__ scales, __half *__restrict__ out, int *status)
+{
+    extern __shared__ __align__(128) uint8_t wsm[]; // [16][K/2 + GEMV_ROW_PAD] weights | [16][G] scales | reduction buffer
+    __shared__ __align__(8) uint64_t bars[GEMV_WARPS * 2];
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int m0 = blockIdx.y * (8 * MB);
+    const int mrows = min(8 * MB, M - m0);
+    const int n0 = blockIdx.x * GEMV_ROWS;
+    const int nkb = K / 128;
+    const int bpw = (nkb + GEMV_WARPS - 1) / GEMV_WARPS;
+    const int kb_lo = min(warp * bpw, nkb), kb_hi = min(kb_lo + bpw, nkb);
+    const int kb_mid = kb_lo + (kb_hi - kb_lo + 1) / 2;
+    const int G = K / group;
+    const int row_bytes = K / 2;
+    const int row_pitch = row_bytes + GEMV_ROW_PAD;
+    const uint32_t wsm_u32 = (uint32_t)__cvta_generic_to_shared(wsm);
+    __half *sc_s = reinterpret_cast<__half *>(wsm + GEMV_ROWS * row_pitch);
+    const int sc_bytes = (GEMV_ROWS * G * 2 + 15) & ~15;
+    float *red = reinterpret_cast<float *>(wsm + GEMV_ROWS * row_pitch + sc_bytes); // [warp][16 rows][8*MB]
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < GEMV_WARPS * 2; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&bars[i])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Scales first (see int4_gemv_kernel: small loads queued behind the weight slab would return last).
+    constexpr int SC_PRE = 4;
+    const int sc_total = GEMV_ROWS * G;
+    __half sc_pre[SC_PRE];
+#pragma unroll
+    for (int j = 0; j < SC_PRE; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < sc_total) sc_pre[j] = __ldg(scales + min((size_t)n0 * G + i, (size_t)N * G - 1));
+    }
+    __syncthreads();
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&bars[warp * 2]);
+    const uint32_t bar1 = bar0 + 8;
+    {
+        const uint32_t bytes0 = (uint32_t)(kb_mid - kb_lo) * 64u, bytes1 = (uint32_t)(kb_hi - kb_mid) * 64u;
+        if (lane == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar0), "r"(bytes0 * 16u) : "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar1), "r"(bytes1 * 16u) : "memory");
+        }
+        __syncwarp();
+        if (lane < GEMV_ROWS) {
+            const int row = min(n0 + lane, N - 1);
+            const uint8_t *src = w + (size_t)row * row_bytes;
+            const uint32_t dst = wsm_u32 + (uint32_t)(lane * row_pitch);
+            if (bytes0) bulk_g2s(dst + kb_lo * 64, src + kb_lo * 64, bytes0, bar0);
+            if (bytes1) bulk_g2s(dst + kb_mid * 64, src + kb_mid * 64, bytes1, bar1);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < SC_PRE; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < sc_total) sc_s[i] = sc_pre[j];
+    }
+    for (int i = threadIdx.x + SC_PRE * blockDim.x; i < sc_total; i += blockDim.x)
+        sc_s[i] = __ldg(scales + min((size_t)n0 * G + i, (size_t)N * G - 1));
+    __syncthreads();
+    const __half *sA = sc_s + g * G;
+    const __half *sB = sc_s + (g + 8) * G;
+    const int bpg = group / 128;
+    const uint8_t *myA = wsm + g * row_pitch + t * 16;
+    const uint8_t *myB = wsm + (g + 8) * row_pitch + t * 16;
+    // Activation row of this lane in row-block j: m0 + 8 j + g, clamped (columns past M are never stored).
+    const uint4 *abase = reinterpret_cast<const uint4 *>(act) + t * 4;
+
+    float tot[MB][4];
+#pragma unroll
+    for (int j = 0; j < MB; ++j) tot[j][0] = tot[j][1] = tot[j][2] = tot[j][3] = 0.f;
+    bool ok = true;
+#pragma unroll 1
+    for (int half = 0; half < 2 && ok; ++half) {
+        const int b0 = half ? kb_mid : kb_lo, b1 = half ? kb_hi : kb_mid;
+        if (b0 >= b1) continue;
+        ok = mbar_wait_warp(half ? bar1 : bar0, 0u, &abort_flag, status, WAIT_EPI_STAGE);
+        if (!ok) break;
+#pragma unroll 1
+        for (int kb = b0; kb < b1; ++kb) {
+            const uint4 qa = *reinterpret_cast<const uint4 *>(myA + kb * 64);
+            const uint4 qb = *reinterpret_cast<const uint4 *>(myB + kb * 64);
+            const uint32_t xa[4] = {qa.x, qa.y, qa.z, qa.w};
+            const uint32_t xb[4] = {qb.x, qb.y, qb.z, qb.w};
+            uint32_t ha[4][4], hb[4][4];
+#pragma unroll
+            for (int wd = 0; wd < 4; ++wd) {
+                unpack8_natural(xa[wd], ha[wd]);
+                unpack8_natural(xb[wd], hb[wd]);
+            }
+            const int si = bpg == 1 ? kb : (int)((unsigned)kb / (unsigned)bpg);
+            const float sa = __half2float(sA[si]);
+            const float sb = __half2float(sB[si]);
+#pragma unroll
+            for (int j = 0; j < MB; ++j) {
+                const int m = m0 + min(8 * j + g, mrows - 1);
+                const uint4 *arow = abase + (size_t)m * (K / 8) + kb * 16;
+                uint4 av[4];
+#pragma unroll
+                for (int wd = 0; wd < 4; ++wd) av[wd] = __ldg(arow + wd);
+                float c0[4], c1[4];
+#pragma unroll
+                for (int wd = 0; wd < 4; ++wd) {
+                    if (wd == 0) {
+                        mma_16816_first(c0, ha[wd][0], hb[wd][0], ha[wd][1], hb[wd][1], av[wd].x, av[wd].y);
+                        mma_16816_first(c1, ha[wd][2], hb[wd][2], ha[wd][3], hb[wd][3], av[wd].z, av[wd].w);
+                    } else {
+                        mma_16816(c0, ha[wd][0], hb[wd][0], ha[wd][1], hb[wd][1], av[wd].x, av[wd].y);
+                        mma_16816(c1, ha[wd][2], hb[wd][2], ha[wd][3], hb[wd][3], av[wd].z, av[wd].w);
+                    }
+                }
+                tot[j][0] = fmaf(sa, c0[0] + c1[0], tot[j][0]);
+                tot[j][1] = fmaf(sa, c0[1] + c1[1], tot[j][1]);
+                tot[j][2] = fmaf(sb, c0[2] + c1[2], tot[j][2]);
+                tot[j][3] = fmaf(sb, c0[3] + c1[3], tot[j][3]);
+            }
+        }
+    }
+
+    // Cross-warp reduction: red[warp][row 0..15][m 0..8*MB)
+    constexpr int MW = 8 * MB;
+#pragma unroll
+    for (int j = 0; j < MB; ++j) {
+        red[(warp * 16 + g) * MW + 8 * j + 2 * t] = tot[j][0];
+        red[(warp * 16 + g) * MW + 8 * j + 2 * t + 1] = tot[j][1];
+        red[(warp * 16 + g + 8) * MW + 8 * j + 2 * t] = tot[j][2];
+        red[(warp * 16 + g + 8) * MW + 8 * j + 2 * t + 1] = tot[j][3];
+    }
+    __syncthreads();
+    if (abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+        return;
+    }
+    for (int i = threadIdx.x; i < 16 * MW; i += blockDim.x) {
+        const int m = i >> 4, r = i & 15; // consecutive threads -> consecutive output columns
+        float sacc = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < GEMV_WARPS; ++wi) sacc += red[(wi * 16 + r) * MW + m];
+        if (m < mrows && n0 + r < N) out[(size_t)(m0 + m) * N + n0 + r] = __float2half_rn(sacc);
+    }
+}
+
 // Any K (even), any group that divides K, any alignment: one thread per output, same arithmetic.
 __global__ void int4_matmul_general_kernel(int M, int N, int K, int group, const __half *__restrict__ act,
                                            const uint8_t *__restrict__ w, const __half *__restrict__ scales,
@@ -372,6 +549,30 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
         int4_matmul_general_kernel<<<(unsigned)grid, block, 0, st>>>(M, N, K, group, (const __half *)act, (const uint8_t *)w,
                                                                      (const __half *)scales, (__half *)out);
         return check_cuda(cudaGetLastError(), "int4 general launch");
+    }
+    if (M > 8) {
+        // Several activation row-blocks per CTA: weights are fetched and unpacked once for up to 64 rows.
+        const int mb = M <= 16 ? 2 : (M <= 32 ? 4 : 8);
+        const size_t smem_mb = (size_t)GEMV_ROWS * (K / 2 + GEMV_ROW_PAD) + (((size_t)GEMV_ROWS * (K / group) * 2 + 15) & ~(size_t)15) +
+                               (size_t)GEMV_WARPS * 16 * 8 * mb * sizeof(float);
+        dim3 grid_mb((unsigned)((N + GEMV_ROWS - 1) / GEMV_ROWS), (unsigned)((M + 8 * mb - 1) / (8 * mb)));
+        cudaError_t e = cudaSuccess;
+#define BTM_LAUNCH_MB(MBV)                                                                                                        \
+    do {                                                                                                                          \
+        if (smem_mb > 48 * 1024)                                                                                                  \
+            e = cudaFuncSetAttribute(int4_gemm_mma_kernel<MBV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);         \
+        if (e == cudaSuccess)                                                                                                     \
+            int4_gemm_mma_kernel<MBV><<<grid_mb, GEMV_WARPS * 32, smem_mb, st>>>(M, N, K, group, (const __half *)act,             \
+                                                                                 (const uint8_t *)w, (const __half *)scales,      \
+                                                                                 (__half *)out, status);                          \
+    } while (0)
+        if (mb == 2) BTM_LAUNCH_MB(2);
+        else if (mb == 4) BTM_LAUNCH_MB(4);
+        else BTM_LAUNCH_MB(8);
+#undef BTM_LAUNCH_MB
+        int rc = check_cuda(e, "cudaFuncSetAttribute(int4_gemm_mma)");
+        if (rc) return rc;
+        return check_cuda(cudaGetLastError(), "int4 gemm launch");
     }
     dim3 grid((unsigned)((N + GEMV_ROWS - 1) / GEMV_ROWS), (unsigned)((M + 7) / 8));
     const bool stage_act = M <= 2;
