@@ -80,6 +80,7 @@ DeviceState *device_state(int device)
     if (check_cuda(cudaMemset(ds->status, 0, sizeof(int)), "cudaMemset(status)")) return nullptr;
     if (configure_gemm_tc_kernels()) return nullptr;
     if (configure_gemm_tc2_kernels()) return nullptr;
+    if (configure_int4_tc_kernels()) return nullptr;
     ds->sm_count = prop.multiProcessorCount;
     ds->ws = nullptr;
     ds->ws_bytes = 0;
@@ -92,6 +93,7 @@ int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, u
 {
     CUtensorMapDataType dt = dtype == BTM_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                              : dtype == BTM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                             : dtype == BTM_U8   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     cuuint64_t dims[3] = {d0, d1, d2};
     cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
@@ -447,6 +449,13 @@ int btm_int4_matmul(int device, void *stream, int M, int N, int K, int group, co
         return set_error(BTM_ERR_INVALID, "int4 matmul: null pointer");
     DeviceState *ds = device_state(device);
     if (!ds) return last_code();
+    // More than 8 activation rows: dequantise into shared memory and multiply on tcgen05 (weights read
+    // from HBM once for up to 128 rows). BTM_FORCE_INT4=mma keeps the mma.sync kernels (tests cover both).
+    const char *force = getenv("BTM_FORCE_INT4");
+    const bool tc_ok = M > 8 && K % 128 == 0 && group % 64 == 0 && N % 8 == 0 && (size_t)64 * (K / group) * 2 <= 8192 &&
+                       (((uintptr_t)act_f16 | (uintptr_t)w_packed | (uintptr_t)out_f16) & 15) == 0 && (((uintptr_t)scales_f16) & 1) == 0 &&
+                       !(force && !strcmp(force, "mma"));
+    if (tc_ok) return launch_int4_gemm_tc((cudaStream_t)stream, M, N, K, group, act_f16, w_packed, scales_f16, out_f16, ds->status);
     return launch_int4_gemv((cudaStream_t)stream, ds->sm_count, M, N, K, group, act_f16, w_packed, scales_f16, out_f16, ds->status);
 }
 

@@ -68,6 +68,9 @@ int launch_int4_dequant(cudaStream_t st, int N, int K, int group, const void *w,
 int launch_int4_unpack(cudaStream_t st, int N, int K, const void *w, void *out);
 int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once per device
 int configure_gemm_tc2_kernels();
+int configure_int4_tc_kernels();
+int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const void *act, const void *w, const void *scales, void *out,
+                        int *status);
 int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
                     const GemmParams &p);
 // Fills `cm` for the destinations in `p` (no-op when p.c_vec_ok == 0: the general store path needs no maps).

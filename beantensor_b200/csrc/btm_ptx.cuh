@@ -90,6 +90,45 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
     return ok != 0;
 }
 
+// try_wait without a suspend hint: returns after a short, implementation-defined time. For hand-offs on
+// the critical path, where the long-sleep form above was measured to add about half a microsecond per
+// wake-up.
+__device__ __forceinline__ bool mbar_try_wait_short(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_short(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+{
+    if (mbar_try_wait_short(bar, parity)) return true;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (true) {
+        if (mbar_try_wait_short(bar, parity)) return true;
+        if ((++spins & 63) == 0) { // look at the abort flag and the clock only now and then
+            if (*abort_flag) return false;
+            if (clock64() - t0 > BTM_WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait_short_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+{
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait_short(bar, parity, abort_flag, status, code) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // Bounded wait. `abort_flag` is a CTA-shared int that any role raises when its own wait
 // ran out; every other waiter then gives up at once instead of running out its own clock.
 template <bool kCluster = false>

@@ -96,3 +96,24 @@ def test_bad_arguments(btm):
         btm.matmul_int4_gpu(act, torch.zeros((16, 50), dtype=torch.uint8, device="cuda"),
                             torch.zeros((16, 0), dtype=torch.float16, device="cuda"),
                             torch.zeros((1, 16), dtype=torch.float16, device="cuda"), 128)
+
+
+@pytest.mark.parametrize("path", ["tensor_core", "mma"])
+@pytest.mark.parametrize("case", [(16, 128, 256, 128), (64, 1088, 1024, 128), (100, 200, 512, 64), (129, 72, 1024, 256), (40, 64, 4096, 128)])
+def test_more_than_eight_rows_both_paths(btm, oracle, case, path, monkeypatch):
+    # M > 8 runs on tcgen05 (weights dequantised into shared memory) unless pinned to the mma.sync kernel.
+    M, N, K, group = case
+    if path == "mma":
+        monkeypatch.setenv("BTM_FORCE_INT4", "mma")
+    w, packed, s, act = make(M, N, K, group, 31 + M)
+    out = gpu_matmul(btm, act, packed, s, group)
+    btm.check_device_status(0)
+    assert not np.isnan(out).any()
+    ref = oracle.int4_matmul(act.view(np.uint16), packed, s.view(np.uint16), group)
+    assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, ref) <= 2e-3
+    if path == "tensor_core":
+        # The tensor-core path multiplies by the dequantised fp16 weights (the btm_int4_dequant values):
+        # against a product of exactly those values only accumulation order and the output rounding differ.
+        dq = oracle.int4_dequant(packed, s.view(np.uint16), group)
+        ref_dq = oracle.gemm(oracle.F16, act.view(np.uint16), np.ascontiguousarray(dq.T))
+        assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, ref_dq) <= 5e-4
