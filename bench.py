@@ -39,8 +39,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (None until a capture of that kernel exists).
 NCU_TRAFFIC = {
-    "gemm_f16_4096": 82.5e6,  # profiles/gemm_tc_f16_4096_1cta.md (69.6 MB read + 12.9 MB written)
-    "int4_gemv_m1": None,
+    "gemm_f16_4096": 105.9e6,  # profiles/gemm_tc2_f16_4096.md (89.0 MB read + 16.9 MB written)
+    "int4_gemv_m1": 23.3e6,  # profiles/int4_gemv_m1.md (read; nothing written back within the kernel)
 }
 
 
