@@ -89,7 +89,7 @@ DeviceState *device_state(int device)
 }
 
 int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
-                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1)
+                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, bool swizzle128)
 {
     CUtensorMapDataType dt = dtype == BTM_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                              : dtype == BTM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -100,7 +100,8 @@ int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, u
     cuuint32_t box[3] = {box0, box1, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = g_encode(out, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return set_error(BTM_ERR_CUDA, "CUDA Error: cuTensorMapEncodeTiled failed with code %d (dims %llu x %llu x %llu)", (int)r,
                          (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2);

@@ -48,7 +48,7 @@ DeviceState *device_state(int device); // NULL + error set on failure
 
 // Encodes a rank-3 tiled tensor map with 128-byte swizzle (dims innermost first).
 int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
-                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1);
+                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, bool swizzle128 = true);
 
 // Launchers (defined next to their kernels). All return a btm_status.
 int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,

@@ -85,24 +85,28 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uin
                  : "memory");
 }
 
-constexpr int GEMV_ROW_PAD = 64; // bytes between staged rows beyond K/2, keeps 128-bit shared loads conflict-free
+constexpr int GEMV_ROW_PAD = 64;      // int4_gemm_mma_kernel: bytes between staged rows beyond K/2
+constexpr int GEMV_PIECE_BYTES = 16 * 128; // int4_gemv_kernel: one TMA piece = 16 rows x 256 k
+constexpr int GEMV_MAX_PIECES = 64;   // K <= 16384 on the fast GEMV path
 
 template <bool kStageAct>
 __global__ void __launch_bounds__(GEMV_WARPS * 32, 5)
-int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act, const uint8_t *__restrict__ w,
+int4_gemv_kernel(const __grid_constant__ CUtensorMap tmW, int M, int N, int K, int group, const __half *__restrict__ act,
                  const __half *__restrict__ scales, __half *__restrict__ out, int *status)
 {
-    // The CTA's whole weight slab (16 rows x K/2 bytes) is requested from HBM at once with bulk async
-    // copies into shared memory: every byte the kernel needs is in flight a few hundred cycles after
-    // the CTA starts, at no register cost. Each warp owns a contiguous quarter of K, split into two
-    // halves with one mbarrier each, and starts computing as soon as its first half has landed.
+    // The CTA's whole weight slab (16 rows x K/2 bytes) is requested from HBM at once: one tiled TMA load
+    // per 256-k piece (a 16-row x 128-byte box, so the row stride is walked by the copy engine and a CTA
+    // issues K/256 loads instead of hundreds of small row copies), one mbarrier per piece. Every byte the
+    // kernel needs is in flight a few hundred cycles after the CTA starts, at no register cost. Each warp
+    // owns a contiguous quarter of the pieces and computes on a piece as soon as it has landed, so the
+    // work left after the last byte arrives is two 128-k blocks per warp.
     // kStageAct (M <= 2): the activations are additionally staged in shared memory, already permuted
     // to the slot order of the unpacked weights, which takes 16 byte-permutes and 4 global loads per
     // 128-k block out of the inner loop. For more rows that copy would not fit beside the weights.
-    // Shared memory: [16][K/2 + GEMV_ROW_PAD] weights | [16][G] fp16 scales | [mrows][K/8 + 1] uint4 staged
+    // Shared memory: [K/256 pieces][16 rows][128 B] weights | [16][G] fp16 scales | [mrows][K/8 + 1] uint4 staged
     // activations (kStageAct only).
     extern __shared__ __align__(128) uint8_t wsm[];
-    __shared__ __align__(8) uint64_t bars[GEMV_WARPS * 2];
+    __shared__ __align__(8) uint64_t bars[GEMV_MAX_PIECES];
     __shared__ float red[GEMV_WARPS * 16 * 8]; // cross-warp reduction [warp][16 rows][8 m]
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -110,22 +114,21 @@ int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act,
     const int m0 = blockIdx.y * 8;
     const int mrows = min(8, M - m0);
     const int n0 = blockIdx.x * GEMV_ROWS;
-    const int nkb = K / 128;                                // 128-k blocks per row
-    const int bpw = (nkb + GEMV_WARPS - 1) / GEMV_WARPS;    // blocks per warp
-    const int kb_lo = min(warp * bpw, nkb), kb_hi = min(kb_lo + bpw, nkb);
-    const int kb_mid = kb_lo + (kb_hi - kb_lo + 1) / 2;     // first half [kb_lo, kb_mid), second [kb_mid, kb_hi)
+    const int nkb = K / 128;                                   // 128-k blocks per row
+    const int npieces = (nkb + 1) / 2;                         // 256-k pieces per row
+    const int ppw = (npieces + GEMV_WARPS - 1) / GEMV_WARPS;   // pieces per warp
+    const int pc_lo = min(warp * ppw, npieces), pc_hi = min(pc_lo + ppw, npieces);
     const int G = K / group;
-    const int row_bytes = K / 2;
-    const int row_pitch = row_bytes + GEMV_ROW_PAD;
     const uint32_t wsm_u32 = (uint32_t)__cvta_generic_to_shared(wsm);
-    __half *sc_s = reinterpret_cast<__half *>(wsm + GEMV_ROWS * row_pitch);               // [16][G]
+    const int w_bytes = npieces * GEMV_PIECE_BYTES;
+    __half *sc_s = reinterpret_cast<__half *>(wsm + w_bytes);                 // [16][G]
     const int sc_bytes = (GEMV_ROWS * G * 2 + 15) & ~15;
-    uint4 *act_s = reinterpret_cast<uint4 *>(wsm + GEMV_ROWS * row_pitch + sc_bytes);     // [mrows][act_pitch]
+    uint4 *act_s = reinterpret_cast<uint4 *>(wsm + w_bytes + sc_bytes);       // [mrows][act_pitch]
     const int act_pitch = K / 8 + 1; // uint4 per staged activation row (+1 keeps rows on different banks)
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        for (int i = 0; i < GEMV_WARPS * 2; ++i)
+        for (int i = 0; i < npieces; ++i)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&bars[i])) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -145,30 +148,27 @@ int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act,
         // (those rows are never stored).
         if (i < sc_total) sc_pre[j] = __ldg(scales + min((size_t)n0 * G + i, (size_t)N * G - 1));
     }
+    __syncthreads(); // mbarriers initialised
+    // One lane per piece: expect 2 KB on the piece's barrier and start its load. Rows past N and k past K
+    // are zero-filled by the copy engine.
+    if (lane < pc_hi - pc_lo) {
+        const int pc = pc_lo + lane;
+        const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&bars[pc]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)GEMV_PIECE_BYTES) : "memory");
+        tma_load_3d(wsm_u32 + (uint32_t)pc * GEMV_PIECE_BYTES, &tmW, pc * 128, n0, 0, bar);
+    }
+    // Programmatic dependent launch: weights and scales are constants, so everything above may run while
+    // the previous kernel on the stream is still finishing. From here on this grid lets its own successor
+    // start, and waits for its predecessor before touching the activations (which a predecessor may have
+    // produced) or writing the output.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if constexpr (kStageAct) {
 #pragma unroll
         for (int j = 0; j < ACT_PRE; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
             // rows m0.. of act are contiguous: uint4 index i of the span
             if (i < act_total) act_pre[j] = __ldg(reinterpret_cast<const uint4 *>(act + (size_t)m0 * K) + i);
-        }
-    }
-    __syncthreads(); // mbarriers initialised
-    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&bars[warp * 2]);
-    const uint32_t bar1 = bar0 + 8;
-    {
-        const uint32_t bytes0 = (uint32_t)(kb_mid - kb_lo) * 64u, bytes1 = (uint32_t)(kb_hi - kb_mid) * 64u; // per row
-        if (lane == 0) {
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar0), "r"(bytes0 * 16u) : "memory");
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar1), "r"(bytes1 * 16u) : "memory");
-        }
-        __syncwarp();
-        if (lane < GEMV_ROWS) {
-            const int row = min(n0 + lane, N - 1); // rows past N re-read the last row; their outputs are not stored
-            const uint8_t *src = w + (size_t)row * row_bytes;
-            const uint32_t dst = wsm_u32 + (uint32_t)(lane * row_pitch);
-            if (bytes0) bulk_g2s(dst + kb_lo * 64, src + kb_lo * 64, bytes0, bar0);
-            if (bytes1) bulk_g2s(dst + kb_mid * 64, src + kb_mid * 64, bytes1, bar1);
         }
     }
     // 8 consecutive activations -> {k0,k4}, {k1,k5}, {k2,k6}, {k3,k7}: the slot order of the unpacked weights
@@ -206,21 +206,19 @@ int4_gemv_kernel(int M, int N, int K, int group, const __half *__restrict__ act,
     const uint4 *arow = reinterpret_cast<const uint4 *>(act + (size_t)(m0 + min(g, mrows - 1)) * K) + t * 4;
     const int bpg = group / 128; // 128-k blocks per scale group
     const uint4 *arow_s = act_s + min(g, mrows - 1) * act_pitch + t * 4;
-    const uint8_t *myA = wsm + g * row_pitch + t * 16;
-    const uint8_t *myB = wsm + (g + 8) * row_pitch + t * 16;
+    const uint8_t *myA = wsm + g * 128 + t * 16;       // + piece * GEMV_PIECE_BYTES + (block in piece) * 64
+    const uint8_t *myB = wsm + (g + 8) * 128 + t * 16;
 
     float tot[4] = {0.f, 0.f, 0.f, 0.f};
-    bool ok = true;
 #pragma unroll 1
-    for (int half = 0; half < 2 && ok; ++half) {
-        const int b0 = half ? kb_mid : kb_lo, b1 = half ? kb_hi : kb_mid;
-        if (b0 >= b1) continue;
-        ok = mbar_wait_warp(half ? bar1 : bar0, 0u, &abort_flag, status, WAIT_EPI_STAGE);
-        if (!ok) break;
-#pragma unroll 4
-        for (int kb = b0; kb < b1; ++kb) {
-            const uint4 qa = *reinterpret_cast<const uint4 *>(myA + kb * 64);
-            const uint4 qb = *reinterpret_cast<const uint4 *>(myB + kb * 64);
+    for (int pc = pc_lo; pc < pc_hi; ++pc) {
+        if (!mbar_wait_warp((uint32_t)__cvta_generic_to_shared(&bars[pc]), 0u, &abort_flag, status, WAIT_EPI_STAGE)) break;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            const int kb = pc * 2 + blk;
+            if (kb >= nkb) break;
+            const uint4 qa = *reinterpret_cast<const uint4 *>(myA + pc * GEMV_PIECE_BYTES + blk * 64);
+            const uint4 qb = *reinterpret_cast<const uint4 *>(myB + pc * GEMV_PIECE_BYTES + blk * 64);
             const uint32_t xa[4] = {qa.x, qa.y, qa.z, qa.w};
             const uint32_t xb[4] = {qb.x, qb.y, qb.z, qb.w};
             const int si = bpg == 1 ? kb : (int)((unsigned)kb / (unsigned)bpg);
@@ -576,20 +574,34 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
     }
     dim3 grid((unsigned)((N + GEMV_ROWS - 1) / GEMV_ROWS), (unsigned)((M + 7) / 8));
     const bool stage_act = M <= 2;
-    size_t smem = (size_t)GEMV_ROWS * (K / 2 + GEMV_ROW_PAD) + (((size_t)GEMV_ROWS * (K / group) * 2 + 15) & ~(size_t)15);
+    const int npieces = (K / 128 + 1) / 2;
+    if (npieces > GEMV_MAX_PIECES) return set_error(BTM_ERR_UNSUPPORTED, "int4 matmul: K=%d is beyond the fast kernel's limit of %d", K, GEMV_MAX_PIECES * 256);
+    CUtensorMap tmW;
+    int rc = encode_tmap_3d(&tmW, BTM_U8, w, (uint64_t)K / 2, (uint64_t)N, 1, (uint64_t)K / 2, (uint64_t)K / 2, 128, GEMV_ROWS, false);
+    if (rc) return rc;
+    size_t smem = (size_t)npieces * GEMV_PIECE_BYTES + (((size_t)GEMV_ROWS * (K / group) * 2 + 15) & ~(size_t)15);
     if (stage_act) smem += (size_t)M * (K / 8 + 1) * sizeof(uint4);
     if (smem > 48 * 1024) {
         cudaError_t e = stage_act ? cudaFuncSetAttribute(int4_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)
                                   : cudaFuncSetAttribute(int4_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-        int rc = check_cuda(e, "cudaFuncSetAttribute(int4_gemv)");
+        rc = check_cuda(e, "cudaFuncSetAttribute(int4_gemv)");
         if (rc) return rc;
     }
-    if (stage_act)
-        int4_gemv_kernel<true><<<grid, GEMV_WARPS * 32, smem, st>>>(M, N, K, group, (const __half *)act, (const uint8_t *)w,
-                                                                    (const __half *)scales, (__half *)out, status);
-    else
-        int4_gemv_kernel<false><<<grid, GEMV_WARPS * 32, smem, st>>>(M, N, K, group, (const __half *)act, (const uint8_t *)w,
-                                                                     (const __half *)scales, (__half *)out, status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(GEMV_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization; // the kernel orders itself with griddepcontrol
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const __half *act_h = (const __half *)act, *sc_h = (const __half *)scales;
+    __half *out_h = (__half *)out;
+    cudaError_t le = stage_act ? cudaLaunchKernelEx(&cfg, int4_gemv_kernel<true>, tmW, M, N, K, group, act_h, sc_h, out_h, status)
+                               : cudaLaunchKernelEx(&cfg, int4_gemv_kernel<false>, tmW, M, N, K, group, act_h, sc_h, out_h, status);
+    if (le != cudaSuccess) return check_cuda(le, "int4 gemv launch");
     return check_cuda(cudaGetLastError(), "int4 gemv launch");
 }
 
