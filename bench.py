@@ -261,21 +261,57 @@ def bench_gemm_single(torch, ops, dtype, n, steps, warmup, sets, dist=None, worl
 
 
 def bench_e2e_gemm(torch, ops, dtype, n, steps, warmup):
-    """Host buffers in pinned memory -> device -> product -> host, every step."""
+    """Host buffers in pinned memory -> device -> product -> host, every step.
+
+    The three legs of a step run on three streams (upload, product, download) over two device buffer
+    sets, so that the upload of step i+1 and the download of step i-1 overlap the product of step i, as a
+    caller feeding a stream of products would arrange it. Every step still uploads both operands and
+    downloads the whole result; the timed region covers all of it."""
     std = n ** -0.5
     ha = synth_f16((n, n), std, 1, 0, dtype).pin_memory()
     hb = synth_f16((n, n), std, 1, 1, dtype).pin_memory()
-    hc = torch.empty((n, n), dtype=dtype).pin_memory()
-    da, db, dc = (torch.empty((n, n), dtype=dtype, device="cuda") for _ in range(3))
+    hc = [torch.empty((n, n), dtype=dtype).pin_memory() for _ in range(2)]
+    dev = [tuple(torch.empty((n, n), dtype=dtype, device="cuda") for _ in range(3)) for _ in range(2)]
+    main = torch.cuda.current_stream()
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+    uploaded = [torch.cuda.Event() for _ in range(2)]
+    computed = [torch.cuda.Event() for _ in range(2)]
+    downloaded = [torch.cuda.Event() for _ in range(2)]
+    for e in downloaded + computed:
+        e.record(main)
 
     def step(i):
-        da.copy_(ha, non_blocking=True)
-        db.copy_(hb, non_blocking=True)
+        s = i & 1
+        da, db, dc = dev[s]
+        up.wait_event(computed[s])       # the product that last read this set's operands is done
+        with torch.cuda.stream(up):
+            da.copy_(ha, non_blocking=True)
+            db.copy_(hb, non_blocking=True)
+            uploaded[s].record(up)
+        main.wait_event(uploaded[s])
+        main.wait_event(downloaded[s])   # the previous result in this set has left the device
         ops.matmul_gpu(da, db, dc)
-        hc.copy_(dc, non_blocking=True)
+        computed[s].record(main)
+        down.wait_event(computed[s])
+        with torch.cuda.stream(down):
+            hc[s].copy_(dc, non_blocking=True)
+            downloaded[s].record(down)
 
-    ms, _, _ = time_region(torch, None, 1, step, steps, warmup)
-    return ms, 2 * n * n * 2, n * n * 2
+    def run(i):
+        step(i)
+
+    for i in range(warmup):
+        run(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(main)
+    for i in range(steps):
+        run(warmup + i)
+    for e in downloaded:
+        main.wait_event(e)  # the last downloads finish before the closing event
+    e1.record(main)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1), 2 * n * n * 2, n * n * 2
 
 
 def bench_int4(torch, ops, peaks, M, steps, warmup):
