@@ -30,6 +30,8 @@ SIGNATURES = {
     "btm_bmm": (_i, [_i, _vp, _i, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
     "btm_int4_matmul": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "btm_int4_dequant": (_i, [_i, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "btm_int4_quantize": (_i, [_i, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "btm_convert": (_i, [_i, _vp, _i, _i, _i64, _vp, _vp]),
     "btm_int4_unpack": (_i, [_i, _vp, _i, _i, _vp, _vp]),
     "btm_gemm_nshard": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, C.POINTER(_vp), _i64, _i, _i]),
     "btm_ipc_alloc": (_i, [_i, _sz, C.POINTER(_vp), C.c_char_p]),

@@ -211,9 +211,7 @@ static int run_f32(DeviceState *ds, cudaStream_t st, const GemmCall &c, void *ws
         return launch_gemm_simt(BTM_F32, st, 1, c.M, c.N, c.K, c.A, c.lda, 0, c.B, c.ldb, 0, c.C[0], c.ldc, 0);
     if (ws_bytes < need) return set_error(BTM_ERR_INVALID, "fp32 matmul: workspace of %zu bytes is smaller than the %zu needed", ws_bytes, need);
     float *a_hi = (float *)ws, *a_lo = a_hi + a_plane, *b_hi = a_lo + a_plane, *b_lo = b_hi + b_plane;
-    int rc = launch_split_tf32(st, (const float *)c.A, c.lda, c.M, c.K, a_hi, a_lo, Kp);
-    if (rc) return rc;
-    rc = launch_split_tf32_transpose(st, (const float *)c.B, c.ldb, c.K, c.N, b_hi, b_lo, Kp);
+    int rc = launch_split_tf32_pair(st, (const float *)c.A, c.lda, c.M, c.K, a_hi, a_lo, (const float *)c.B, c.ldb, c.N, b_hi, b_lo, Kp);
     if (rc) return rc;
     // The B box is one whole tile (bn rows), so the tile width is chosen here: 128 columns, or 64
     // when that leaves SMs without a tile.
@@ -478,6 +476,26 @@ int btm_int4_unpack(int device, void *stream, int N, int K, const void *w_packed
     DeviceState *ds = device_state(device);
     if (!ds) return last_code();
     return launch_int4_unpack((cudaStream_t)stream, N, K, w_packed, out_i8);
+}
+
+int btm_convert(int device, void *stream, int src_dtype, int dst_dtype, int64_t n, const void *src, void *dst)
+{
+    if (n < 0) return set_error(BTM_ERR_INVALID, "convert: negative element count");
+    if (n > 0 && (!src || !dst)) return set_error(BTM_ERR_INVALID, "convert: null pointer");
+    if (src_dtype == dst_dtype) return set_error(BTM_ERR_INVALID, "convert: source and destination dtype are the same");
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    return launch_convert((cudaStream_t)stream, src_dtype, dst_dtype, n, src, dst);
+}
+
+int btm_int4_quantize(int device, void *stream, int N, int K, int group, const void *w_f16, void *out_packed, void *out_scales_f16)
+{
+    if (N < 0 || K < 0) return set_error(BTM_ERR_INVALID, "int4 quantise: negative dimension");
+    if (group <= 0 || group % 2 || (K % group) != 0) return set_error(BTM_ERR_INVALID, "int4 quantise: K=%d must be a multiple of the even group=%d", K, group);
+    if ((long long)N * K > 0 && (!w_f16 || !out_packed || !out_scales_f16)) return set_error(BTM_ERR_INVALID, "int4 quantise: null pointer");
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    return launch_int4_quantize((cudaStream_t)stream, N, K, group, w_f16, out_packed, out_scales_f16);
 }
 
 int btm_ipc_alloc(int device, size_t bytes, void **ptr, unsigned char handle[64])

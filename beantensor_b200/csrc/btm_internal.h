@@ -60,12 +60,16 @@ int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K,
                      long long strideC);
 int launch_split_tf32(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
                       float *dst_lo, long long ld_dst);
+int launch_split_tf32_pair(cudaStream_t st, const float *A, long long lda, int M, int K, float *a_hi, float *a_lo, const float *B,
+                           long long ldb, int N, float *b_hi, float *b_lo, long long Kp);
 int launch_split_tf32_transpose(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
                                 float *dst_lo, long long ld_dst);
 int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act,
                      const void *w, const void *scales, void *out, int *status);
 int launch_int4_dequant(cudaStream_t st, int N, int K, int group, const void *w, const void *scales, void *out);
 int launch_int4_unpack(cudaStream_t st, int N, int K, const void *w, void *out);
+int launch_convert(cudaStream_t st, int src_dtype, int dst_dtype, long long n, const void *src, void *dst);
+int launch_int4_quantize(cudaStream_t st, int N, int K, int group, const void *w, void *packed, void *scales);
 int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once per device
 int configure_gemm_tc2_kernels();
 int configure_int4_tc_kernels();

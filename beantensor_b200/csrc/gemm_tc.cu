@@ -295,6 +295,57 @@ __global__ void split_tf32_transpose_kernel(const float *__restrict__ src, long 
     }
 }
 
+// Both operands in one launch (the 1024^3 product is launch-bound: one kernel less is ~5 us of 30):
+// the first `tiles_a` blocks split 32 x 32 tiles of A in place, the others split and transpose tiles of B.
+__global__ void split_tf32_pair_kernel(const float *__restrict__ A, long long lda, int M, int K, float *__restrict__ a_hi,
+                                       float *__restrict__ a_lo, const float *__restrict__ B, long long ldb, int N,
+                                       float *__restrict__ b_hi, float *__restrict__ b_lo, long long Kp, int tiles_a, int kt)
+{
+    __shared__ float tile[32][33];
+    const int blk = blockIdx.x;
+    if (blk < tiles_a) {
+        const int r0 = (blk / kt) * 32, c0 = (blk % kt) * 32;
+        for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+            const int r = r0 + i, c = c0 + threadIdx.x;
+            if (r < M && c < Kp) {
+                const float x = c < K ? A[(long long)r * lda + c] : 0.0f;
+                const float h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+                a_hi[(long long)r * Kp + c] = h;
+                a_lo[(long long)r * Kp + c] = x - h;
+            }
+        }
+        return;
+    }
+    const int b = blk - tiles_a;
+    const int c0 = (b / kt) * 32, r0 = (b % kt) * 32; // c0: column of B (output row), r0: row of B = k
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int r = r0 + i, c = c0 + threadIdx.x;
+        tile[i][threadIdx.x] = (r < K && c < N) ? B[(long long)r * ldb + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int c = c0 + i, r = r0 + threadIdx.x;
+        if (c < N && r < Kp) {
+            const float x = tile[threadIdx.x][i];
+            const float h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+            b_hi[(long long)c * Kp + r] = h;
+            b_lo[(long long)c * Kp + r] = x - h;
+        }
+    }
+}
+
+int launch_split_tf32_pair(cudaStream_t st, const float *A, long long lda, int M, int K, float *a_hi, float *a_lo, const float *B,
+                           long long ldb, int N, float *b_hi, float *b_lo, long long Kp)
+{
+    const long long kt = (Kp + 31) / 32;
+    const long long tiles_a = (long long)((M + 31) / 32) * kt, tiles_b = (long long)((N + 31) / 32) * kt;
+    if (tiles_a + tiles_b == 0) return BTM_OK;
+    if (tiles_a + tiles_b > 0x7FFFFFFFLL) return set_error(BTM_ERR_UNSUPPORTED, "fp32 matmul: operands too large for the split pass");
+    split_tf32_pair_kernel<<<(unsigned)(tiles_a + tiles_b), dim3(32, 8), 0, st>>>(A, lda, M, K, a_hi, a_lo, B, ldb, N, b_hi, b_lo, Kp,
+                                                                                 (int)tiles_a, (int)kt);
+    return check_cuda(cudaGetLastError(), "split_tf32_pair launch");
+}
+
 int launch_split_tf32_transpose(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
                                 float *dst_lo, long long ld_dst)
 {

@@ -138,6 +138,34 @@ def unpack_int4_gpu(w_packed: torch.Tensor, out: torch.Tensor) -> None:
     raise_for_status(rc)
 
 
+def quantize_int4_gpu(w: torch.Tensor, w_packed: torch.Tensor, scales: torch.Tensor, group: int = 128) -> None:
+    """fp16 weights [N,K] -> packed nibbles [N,K/2] + fp16 scales [N,K/group] (max-abs / 7 per group)."""
+    dev = _require_gpu(w, w_packed, scales)
+    N, K = w.shape
+    if w.dtype != torch.float16 or scales.dtype != torch.float16 or w_packed.dtype != torch.uint8:
+        raise ValueError("quantize_int4_gpu: Float16 weights and scales, byte output")
+    if group <= 0 or K % group or w_packed.shape != (N, K // 2) or scales.shape != (N, K // group):
+        raise ValueError("quantize_int4_gpu: shape mismatch")
+    for t in (w, w_packed, scales):
+        if not t.is_contiguous():
+            raise ValueError("quantize_int4_gpu: tensors must be contiguous")
+    rc = _lib.lib().btm_int4_quantize(dev, _stream(), N, K, group, w.data_ptr(), w_packed.data_ptr(), scales.data_ptr())
+    raise_for_status(rc)
+
+
+def convert_gpu(src: torch.Tensor, dst: torch.Tensor) -> None:
+    """dst = dtype conversion of src (Float32 / Float16 / BFloat16, round to nearest even); the matmul-side
+    counterpart of the reference's convert_gpu (Tensor/TensorOps.cu:315-365), out of place."""
+    dev = _require_gpu(src, dst)
+    if src.shape != dst.shape or not src.is_contiguous() or not dst.is_contiguous():
+        raise ValueError("convert_gpu: shapes differ or tensors are not contiguous")
+    if src.dtype not in _DT or dst.dtype not in _DT:
+        from .errors import NotImplementedOp
+        raise NotImplementedOp(f"convert_gpu: {src.dtype} -> {dst.dtype} is not supported")
+    rc = _lib.lib().btm_convert(dev, _stream(), _DT[src.dtype], _DT[dst.dtype], src.numel(), src.data_ptr(), dst.data_ptr())
+    raise_for_status(rc)
+
+
 def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """User-level wrapper in the style of the reference's Ops::add sketch
     (Ops/Elementwise/Add/Add.h:28-73): checks, allocates the result, dispatches by rank."""

@@ -174,6 +174,19 @@ int btm_int4_matmul(int device, void *stream, int M, int N, int K, int group, co
 int btm_int4_dequant(int device, void *stream, int N, int K, int group, const void *w_packed,
                      const void *scales_f16, void *out_f16);
 
+/* Group quantiser, the producer of the packed format: for every row n and group g of `group` consecutive k,
+ * S[n,g] = f16_rne(max|w| / 7) (1 when the group is all zero) and
+ * W[n,k] = clamp(rint(float(w[n,k]) / float(S[n,g])), -8, 7) with round-half-to-even, packed two per byte.
+ * fp16 in, bytes [N,K/2] and fp16 scales [N,K/group] out. The reference has no quantised type; this is
+ * the convert_gpu() case (Tensor/TensorOps.cu:315-365) towards the appended dtype. */
+int btm_int4_quantize(int device, void *stream, int N, int K, int group, const void *w_f16, void *out_packed,
+                      void *out_scales_f16);
+
+/* Element-wise dtype conversion among BTM_F32, BTM_F16 and BTM_BF16 with round-to-nearest-even, n contiguous
+ * elements. Extends the reference's convert_gpu(), which handles Float32 <-> BFloat16 only and leaves other
+ * pairs untouched (Tensor/TensorOps.cu:337-345); rounding as its __floats2bfloat162_rn (:72). */
+int btm_convert(int device, void *stream, int src_dtype, int dst_dtype, int64_t n, const void *src, void *dst);
+
 /* Unpack only: int8 out[n,k] = W[n,k] in [-8,7]. */
 int btm_int4_unpack(int device, void *stream, int N, int K, const void *w_packed, void *out_i8);
 

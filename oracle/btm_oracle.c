@@ -479,3 +479,35 @@ int btmo_gemm_f32_threads(int64_t M, int64_t N, int64_t K, const float *A, const
     for (int t = 0; t < started; ++t) pthread_join(tids[t], NULL);
     return 0;
 }
+
+/* ------------------------------------------------------------------------------------
+ * int4 group quantiser (the producer of the packed format; this build's own convention,
+ * the reference has no quantised type): per row n and group g,
+ *   S[n,g] = f16_rne(max|w| / 7) in binary32 arithmetic, 1 when the group is all zero;
+ *   W[n,k] = clamp(rint(float(w) / float(S)), -8, 7), rint = round half to even.
+ * ---------------------------------------------------------------------------------- */
+void btmo_int4_quantize(const uint16_t *w_f16, int64_t N, int64_t K, int64_t group, uint8_t *packed, uint16_t *scales_f16)
+{
+    int64_t G = K / group;
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t g = 0; g < G; ++g) {
+            const uint16_t *src = w_f16 + n * K + g * group;
+            float amax = 0.0f;
+            for (int64_t k = 0; k < group; ++k) {
+                float v = fabsf(btmo_f16_to_f32(src[k]));
+                if (v > amax) amax = v;
+            }
+            uint16_t sh = btmo_f64_to_f16_rne((double)(amax / 7.0f));
+            if (btmo_f16_to_f32(sh) == 0.0f) sh = 0x3C00u;
+            float s = btmo_f16_to_f32(sh);
+            scales_f16[n * G + g] = sh;
+            for (int64_t k = 0; k < group; k += 2) {
+                float q0 = rintf(btmo_f16_to_f32(src[k]) / s), q1 = rintf(btmo_f16_to_f32(src[k + 1]) / s);
+                if (q0 < -8.0f) q0 = -8.0f;
+                if (q0 > 7.0f) q0 = 7.0f;
+                if (q1 < -8.0f) q1 = -8.0f;
+                if (q1 > 7.0f) q1 = 7.0f;
+                packed[n * (K / 2) + (g * group + k) / 2] = (uint8_t)(((int)q0 & 0xF) | (((int)q1 & 0xF) << 4));
+            }
+        }
+}

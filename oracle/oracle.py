@@ -55,6 +55,7 @@ def lib() -> C.CDLL:
         L.btmo_int4_unpack.argtypes = [vp, i64, i64, vp]
         L.btmo_int4_dequant.argtypes = [vp, vp, i64, i64, i64, vp]
         L.btmo_int4_matmul.argtypes = [i64, i64, i64, i64, vp, vp, vp, vp, C.c_int]
+        L.btmo_int4_quantize.argtypes = [vp, i64, i64, i64, vp, vp]
         L.btmo_rel_frobenius.argtypes = [vp, C.c_int, vp, C.c_size_t]
         L.btmo_rel_frobenius.restype = dbl
         L.btmo_widen.argtypes = [vp, C.c_int, C.c_size_t, vp]
@@ -131,6 +132,15 @@ def int4_matmul(act_f16: np.ndarray, packed: np.ndarray, scales_f16: np.ndarray,
                                 _p(np.ascontiguousarray(scales_f16)), _p(out), threads())
     assert rc == 0
     return out
+
+
+def int4_quantize(w_f16: np.ndarray, group: int):
+    """fp16 bit patterns [N,K] -> (packed [N,K/2] bytes, scales [N,K/group] fp16 bit patterns)."""
+    N, K = w_f16.shape
+    packed = np.zeros((N, K // 2), dtype=np.uint8)
+    scales = np.zeros((N, K // group), dtype=np.uint16)
+    lib().btmo_int4_quantize(_p(np.ascontiguousarray(w_f16)), N, K, group, _p(packed), _p(scales))
+    return packed, scales
 
 
 def rel_frobenius(X: np.ndarray, dtype: int, R: np.ndarray) -> float:

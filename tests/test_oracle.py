@@ -91,3 +91,17 @@ def test_cpu_baseline_body_matches_oracle(oracle):
     B = synth.uniform((80, 72), -1, 1, 1, 1).astype(np.float32)
     C = oracle.gemm_f32_threads(A, B, 3)
     assert oracle.rel_frobenius(C, oracle.F32, oracle.gemm(oracle.F32, A, B)) < 1e-6
+
+
+def test_quantiser_restatement_against_numpy(oracle):
+    from beantensor_b200 import synth
+    N, K, group = 12, 256, 64
+    w = synth.normal((N, K), 0.05, 77, 0).astype(np.float16)
+    w[3, :group] = 0
+    packed, scales = oracle.int4_quantize(w.view(np.uint16), group)
+    wf = w.astype(np.float32).reshape(N, K // group, group)
+    s = (np.abs(wf).max(axis=2) / np.float32(7.0)).astype(np.float16)
+    s[s == 0] = np.float16(1.0)
+    assert np.array_equal(scales, s.view(np.uint16))
+    q = np.clip(np.rint(wf / s.astype(np.float32)[:, :, None]), -8, 7).astype(np.int8).reshape(N, K)
+    assert np.array_equal(oracle.int4_unpack(packed), q)
