@@ -170,3 +170,39 @@ def test_transposed_b_entry_point(btm, oracle, dtype):
     a = torch.zeros((8, 12), dtype=torch_dtype(dtype), device="cuda")
     rc = L.btm_gemm_bt(0, None, dtype, 8, 8, 12, a.data_ptr(), 12, a.data_ptr(), 12, a.data_ptr(), 8)
     assert rc == _lib.ERR_UNSUPPORTED
+
+
+def test_concurrent_callers_on_their_own_streams(btm, oracle):
+    # The reference serves operators from pool threads (Helper/Threads/CPUThreading.h:37-56): calls for
+    # different tensors may arrive concurrently. Four host threads, each with its own stream and operands.
+    import threading
+    import torch
+    dtype = _lib.F16
+    shapes = [(384, 512, 256), (1000, 1000, 992), (257, 513, 136), (512, 2048, 512)]
+    results, errors = {}, []
+
+    def worker(i):
+        try:
+            M, N, K = shapes[i]
+            A, B = gemm_inputs(dtype, M, N, K, 50 + i)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                a, b = to_gpu(A, dtype), to_gpu(B, dtype)
+                out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+                for _ in range(10):
+                    btm.matmul_gpu(a, b, out)
+                stream.synchronize()
+            results[i] = (to_host_bits(out, dtype), A, B)
+        except Exception as e:  # surfaced below, in the main thread
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    btm.check_device_status(0)
+    for i in range(4):
+        got, A, B = results[i]
+        assert oracle.rel_frobenius(got, dtype, oracle.gemm(dtype, A, B)) <= TOL[dtype], shapes[i]
