@@ -147,7 +147,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-// Warp-collective form for the epilogue warps: one lane waits, the verdict is broadcast, so 31 lanes
+// Warp-collective form for the epilogue warps: one lane waits, the outcome is broadcast, so 31 lanes
 // per warp do not poll. All 32 lanes must call it.
 template <bool kCluster = false>
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)

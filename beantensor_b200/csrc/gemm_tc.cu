@@ -227,7 +227,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const TileCoord tc = decode_tile<BN>(p, tile);
             const int acc = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-            // One lane waits and broadcasts the verdict: tcgen05.ld below needs the whole warp.
+            // One lane waits and broadcasts the outcome: tcgen05.ld below needs the whole warp.
             if (!mbar_wait_warp(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL)) break;
             tc_fence_after();
             epilogue_band<DT>(p, cmaps, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN), tc.m * BM + quad * 32, tc.n0,
