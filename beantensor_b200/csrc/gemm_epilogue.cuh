@@ -4,9 +4,10 @@
 // band of the tile. It reads 32 accumulator columns at a time with tcgen05.ld, rounds to the output
 // type and writes them into a warp-private shared-memory tile of 32 rows x 128 bytes laid out with
 // the 128-byte swizzle (conflict-free 16-byte stores); one lane then hands the tile to a TMA store
-// (cp.async.bulk.tensor ... global.shared::cta), once per destination copy of C. The TMA unit clips
+// (cp.async.bulk.tensor ... global.shared::cta). The TMA unit clips
 // rows and columns beyond the matrix, so the band needs no predicates, and C is written in whole
-// 128-byte lines. Two tiles per warp alternate so that a store drains while the next is filled.
+// 128-byte lines. Two tiles per warp alternate so that a store drains while the next is filled. With
+// several destination copies of C the peers are written by epilogue_band_multi (below).
 // General path (unaligned C): per-thread row stores, as the kernels did originally.
 #pragma once
 #include <cuda_bf16.h>
@@ -83,6 +84,77 @@ __device__ __forceinline__ void store_row_direct(const GemmParams &p, const uint
     }
 }
 
+// Band drain when C has several destination copies (the fused all-gather of the N-sharded product).
+// 128 output columns at a time: both staging tiles are filled, the local copy goes out as two TMA
+// stores, and the peers are written with plain 16-byte stores from registers, laid out so that one
+// warp instruction covers two rows x 256 contiguous bytes. Peer traffic crosses NVLink, where 256-byte
+// contiguous writes pack better than the 128-byte rows of a staging tile, and stores from registers
+// are posted: the warp never waits for a peer before it frees the accumulator.
+template <int DT>
+__device__ __forceinline__ void epilogue_band_multi(const GemmParams &p, const StoreMaps &cmaps, uint32_t tmem_band, int row0,
+                                                    int col_first, int bn, int batch, uint32_t epi_smem, uint32_t &tile_count, int lane)
+{
+    const uint32_t swz = (uint32_t)(lane & 7);
+#pragma unroll 1
+    for (int c = 0; c < bn / 128; ++c) {
+        tile_count += 2;
+        // Both staging tiles are about to be rewritten: the local stores of the previous pair must have read them.
+        if (lane == 0) bulk_wait_read<0>();
+        __syncwarp();
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const uint32_t row_addr = epi_smem + (uint32_t)t * EPI_TILE_BYTES + (uint32_t)lane * 128u;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t v[32], q[16];
+                tmem_ld_32x32(tmem_band + (uint32_t)(c * 128 + t * 64 + h * 32), v);
+                tmem_ld_wait();
+                pack16<DT>(v, q);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    st_shared_v4(row_addr + (((uint32_t)(h * 4 + j) ^ swz) << 4), q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
+            }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int col = col_first + c * 128;
+        if (lane == 0) {
+            if (row0 < p.M && col < p.N) tma_store_3d(&cmaps.m[0], epi_smem, (int)p.col0 + col, row0, batch);
+            if (row0 < p.M && col + 64 < p.N) tma_store_3d(&cmaps.m[0], epi_smem + EPI_TILE_BYTES, (int)p.col0 + col + 64, row0, batch);
+            bulk_commit();
+        }
+        // Peers: lane l owns the 16-byte chunk (l & 15) of the 256-byte row pieces of rows 2 i + (l >> 4).
+        const int chunk = lane & 15, tsel = chunk >> 3, cj = chunk & 7;
+        uint4 regs[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int r = 2 * i + (lane >> 4);
+            const uint32_t a = epi_smem + (uint32_t)tsel * EPI_TILE_BYTES + (uint32_t)r * 128u + ((((uint32_t)cj) ^ (uint32_t)(r & 7)) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(regs[i].x), "=r"(regs[i].y), "=r"(regs[i].z), "=r"(regs[i].w) : "r"(a));
+        }
+        const int ccol = col + chunk * 8; // first of this lane's 8 columns
+        const long long base = (long long)batch * p.strideC + p.col0 + ccol;
+        for (int d = 1; d < p.ndst; ++d) {
+            uint16_t *dst = reinterpret_cast<uint16_t *>(p.C[d]);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int row = row0 + 2 * i + (lane >> 4);
+                if (row < p.M) {
+                    uint16_t *q = dst + base + (long long)row * p.ldc;
+                    if (ccol + 8 <= p.N) {
+                        *reinterpret_cast<uint4 *>(q) = regs[i];
+                    } else {
+                        const uint32_t w[4] = {regs[i].x, regs[i].y, regs[i].z, regs[i].w};
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (ccol + e < p.N) q[e] = (uint16_t)((e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xFFFFu));
+                    }
+                }
+            }
+        }
+    }
+}
+
 // Drains one 32-row band (this warp's tensor-memory quadrant) of a finished tile.
 //   tmem_band   tensor-memory address of the band's first accumulator column (lane bits included)
 //   row0        first output row of the band; col_first first output column of the tile; bn its width
@@ -108,6 +180,12 @@ __device__ __forceinline__ void epilogue_band(const GemmParams &p, const StoreMa
         return;
     }
     const uint32_t swz = (uint32_t)(lane & 7);
+    if constexpr (DT != BTM_F32) {
+        if (p.ndst > 1 && (bn & 127) == 0) {
+            epilogue_band_multi<DT>(p, cmaps, tmem_band, row0, col_first, bn, batch, epi_smem, tile_count, lane);
+            return;
+        }
+    }
 #pragma unroll 1
     for (int c = 0; c < bn / kColsPerTile; ++c) {
         const uint32_t buf = epi_smem + (tile_count & 1u) * EPI_TILE_BYTES;
@@ -138,14 +216,7 @@ __device__ __forceinline__ void epilogue_band(const GemmParams &p, const StoreMa
         __syncwarp();
         const int col = col_first + c * kColsPerTile;
         if (lane == 0) {
-            if (row0 < p.M && col < p.N) {
-                const int x = (int)p.col0 + col;
-#pragma unroll
-                for (int d = 0; d < kMaxDst; ++d) {
-                    if (d >= p.ndst) break;
-                    tma_store_3d(&cmaps.m[d], buf, x, row0, batch);
-                }
-            }
+            if (row0 < p.M && col < p.N) tma_store_3d(&cmaps.m[0], buf, (int)p.col0 + col, row0, batch);
             bulk_commit(); // an empty group when nothing was stored keeps the buffer accounting uniform
         }
     }
