@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 
@@ -183,6 +184,16 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
     p.col0 = c.col0;
     p.c_vec_ok = vec ? 1 : 0;
     p.status = ds->status;
+    if (c.ndst > 1) {
+        // Peer stores of a tile are spread over part of the next tile's main loop instead of leaving the
+        // SM as one burst. Unit: SM cycles per 64-deep k-block (a k-block of a 256 x 256 pair tile takes
+        // 650-750). Measured on 16384^3 bf16: at 8 ranks 500 gives 1.05 ms against 1.12-1.22 ms unpaced
+        // and 100-400 are no better than unpaced; at 4 ranks pacing does not help, so it is off below 8.
+        // BTM_NSHARD_PACE overrides (0 = off).
+        const char *pace = getenv("BTM_NSHARD_PACE");
+        const long long per_kb = pace ? atoll(pace) : (c.ndst >= 8 ? 500 : 0);
+        p.pace_cycles = (int)std::min<long long>(per_kb * ((c.K + 63) / 64), 1LL << 30);
+    }
     // CTA pairs (256 x 256 tiles, B shared between two SMs) once there is enough work to fill a good
     // part of the machine; single CTAs (128 x 256 or 128 x 128) for small outputs.
     // BTM_FORCE_KERNEL=1cta|2cta overrides the choice (used by the tests to cover both on every shape).

@@ -24,6 +24,7 @@ struct GemmParams {
     long long ldc;     // elements
     long long strideC; // elements between products
     long long col0;    // first output column of this launch inside C
+    int pace_cycles;   // >0: peer stores of one tile are spread over this many SM cycles (several destinations only)
     int c_vec_ok;      // 16-byte vector stores into C are legal
     int *status;       // device status word (bounded waits report here)
 };

@@ -95,6 +95,12 @@ __device__ __forceinline__ void epilogue_band_multi(const GemmParams &p, const S
                                                     int col_first, int bn, int batch, uint32_t epi_smem, uint32_t &tile_count, int lane)
 {
     const uint32_t swz = (uint32_t)(lane & 7);
+    // Pacing: the peer stores of this tile are issued in (bn / 128) x (ndst - 1) batches, batch j not
+    // before t0 + j x step, so that they leave the SM spread over the time the next tile's main loop
+    // takes instead of as one burst.
+    const long long t0 = clock64();
+    const long long step = p.pace_cycles > 0 ? (long long)p.pace_cycles / ((bn / 128) * (p.ndst - 1)) : 0;
+    int batch_no = 0;
 #pragma unroll 1
     for (int c = 0; c < bn / 128; ++c) {
         tile_count += 2;
@@ -134,8 +140,12 @@ __device__ __forceinline__ void epilogue_band_multi(const GemmParams &p, const S
         }
         const int ccol = col + chunk * 8; // first of this lane's 8 columns
         const long long base = (long long)batch * p.strideC + p.col0 + ccol;
-        for (int d = 1; d < p.ndst; ++d) {
+        for (int d = 1; d < p.ndst; ++d, ++batch_no) {
             uint16_t *dst = reinterpret_cast<uint16_t *>(p.C[d]);
+            if (step > 0) {
+                const long long due = t0 + step * batch_no;
+                while (clock64() < due) __nanosleep(256); // bounded: `due` is at most pace_cycles away
+            }
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const int row = row0 + 2 * i + (lane >> 4);
