@@ -90,7 +90,7 @@ DeviceState *device_state(int device)
 }
 
 int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
-                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, bool swizzle128)
+                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, int swizzle)
 {
     CUtensorMapDataType dt = dtype == BTM_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                              : dtype == BTM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -101,7 +101,7 @@ int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, u
     cuuint32_t box[3] = {box0, box1, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = g_encode(out, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return set_error(BTM_ERR_CUDA, "CUDA Error: cuTensorMapEncodeTiled failed with code %d (dims %llu x %llu x %llu)", (int)r,
@@ -462,10 +462,13 @@ int btm_int4_matmul(int device, void *stream, int M, int N, int K, int group, co
     // More than 8 activation rows: dequantise into shared memory and multiply on tcgen05 (weights read
     // from HBM once for up to 128 rows). BTM_FORCE_INT4=mma keeps the mma.sync kernels (tests cover both).
     const char *force = getenv("BTM_FORCE_INT4");
-    const bool tc_ok = M > 8 && K % 128 == 0 && group % 64 == 0 && N % 8 == 0 && (size_t)64 * (K / group) * 2 <= 8192 &&
-                       (((uintptr_t)act_f16 | (uintptr_t)w_packed | (uintptr_t)out_f16) & 15) == 0 && (((uintptr_t)scales_f16) & 1) == 0 &&
+    const bool tc_ok = M > 8 && N > 0 && K >= 128 && K % 128 == 0 && group % 64 == 0 &&
+                       (((uintptr_t)act_f16 | (uintptr_t)w_packed) & 15) == 0 && (((uintptr_t)scales_f16 | (uintptr_t)out_f16) & 1) == 0 &&
                        !(force && !strcmp(force, "mma"));
-    if (tc_ok) return launch_int4_gemm_tc((cudaStream_t)stream, M, N, K, group, act_f16, w_packed, scales_f16, out_f16, ds->status);
+    if (tc_ok) {
+        int rc = launch_int4_gemm_tc((cudaStream_t)stream, M, N, K, group, act_f16, w_packed, scales_f16, out_f16, ds->status, ds->sm_count);
+        if (rc != BTM_ERR_UNSUPPORTED) return rc; // unsupported: scales too many for shared memory, nothing launched
+    }
     return launch_int4_gemv((cudaStream_t)stream, ds->sm_count, M, N, K, group, act_f16, w_packed, scales_f16, out_f16, ds->status);
 }
 

@@ -47,9 +47,9 @@ int set_error(int code, const char *fmt, ...);
 int check_cuda(cudaError_t e, const char *what);
 DeviceState *device_state(int device); // NULL + error set on failure
 
-// Encodes a rank-3 tiled tensor map with 128-byte swizzle (dims innermost first).
+// Encodes a rank-3 tiled tensor map (dims innermost first). swizzle: 0 none, 1 128-byte, 2 64-byte.
 int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
-                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, bool swizzle128 = true);
+                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, int swizzle = 1);
 
 // Launchers (defined next to their kernels). All return a btm_status.
 int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
@@ -75,7 +75,7 @@ int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once pe
 int configure_gemm_tc2_kernels();
 int configure_int4_tc_kernels();
 int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const void *act, const void *w, const void *scales, void *out,
-                        int *status);
+                        int *status, int sm_count);
 int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
                     const GemmParams &p);
 // Fills `cm` for the destinations in `p` (no-op when p.c_vec_ok == 0: the general store path needs no maps).

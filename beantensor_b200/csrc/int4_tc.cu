@@ -3,25 +3,28 @@
 // i.e. the weights are dequantised exactly as btm_int4_dequant defines them and the product runs as an
 // fp16 tcgen05 matmul with fp32 accumulation in tensor memory.
 //
-// One CTA owns 64 weight rows (output columns) and all activation rows of the pass. Per 64-k block:
-//   warp 0      TMA: the packed weights arrive as 256-k chunks (64 rows x 128 B, 128-byte swizzle) in
-//               a small ring; the activation tile (BM rows x 64 k, K-major, 128-byte swizzle) goes
-//               straight into the operand stage;
-//   warps 2-5   dequantise: one 128-bit shared load (32 nibbles) per thread and block, unpack to exact
-//               fp16 integers in natural k order, multiply by the group scale, and write the
-//               64 x 64 fp16 tile in the K-major 128-byte-swizzled layout the tensor core reads;
-//   warp 1      issues tcgen05.mma (M = 128, N = 64, both operands K-major) once both halves of the
-//               stage are ready; tcgen05.commit frees the stage.
-// After the last block warps 2-5 drain the accumulator with the shared TMA-store epilogue; rows past M
-// are clipped by the store. The HBM traffic is the packed weights once (N*K/2 bytes) plus scales;
-// activations are re-read per CTA from L2 (N/64 x M x K x 2 bytes).
+// The product is computed transposed: the 128 dequantised weight rows of a CTA are the tensor core's
+// A operand (its full 128-row datapath), the activation rows are the B operand (UMMA N = 64 or 128), so
+// no tensor-core row is spent on padding when M is small. K is split over the CTAs of a cluster, which
+// puts two or three times as many CTAs on the machine as there are 128-row weight tiles (86 for
+// N = 11008) and divides the activation bytes a CTA pulls from L2 by the same factor; the partial
+// accumulators meet in the shared memory of the cluster's first CTA.
 //
-// Measured (N=11008, K=4096, M=64): 43 us with HBM 6.5 % and the tensor pipe 12 % busy. The time follows
-// the depth of the activation ring (3 stages 73 us, 4 stages 50 us, 8 stages 43 us) and not the number of
-// proxy fences or hand-offs per chunk (one per 256-k chunk instead of four: no gain), the K order per CTA,
-// or the dequantisation arithmetic (removed: 37 us): the 64-row x 128-byte activation tiles, which every
-// CTA re-reads from L2, arrive with microseconds of latency, and with two CTAs per SM there is no shared
-// memory left for a deeper ring. Fewer, wider CTAs (more weight rows per activation tile) are the way out.
+// Roles in a CTA (7 warps), per 128-k unit of its K slice:
+//   warp 0      TMA: packed weights, 128 rows x 64 B (64-byte swizzle), ring of 3-4 units;
+//   warp 2      TMA: activation tiles, MB rows x 64 k (K-major, 128-byte swizzle), two per unit;
+//   warps 3-10  dequantise: thread = (weight row, 64-k block of the unit); two 128-bit shared loads,
+//               unpack to exact fp16 integers in natural k order, multiply by the group scale, write
+//               the row of the 128 x 64 fp16 tile in the K-major 128-byte-swizzled layout the tensor
+//               core reads. The dequantisation is the critical resource (about two instructions per
+//               weight), hence eight warps per CTA and two CTAs per SM;
+//   warp 1      tcgen05.mma (M = 128, N = MB, both operands K-major); tcgen05.commit frees the stages.
+// Then every CTA reads its accumulator (lane = weight row, column = activation row); CTAs 1.. of the
+// cluster store theirs into CTA 0's shared memory (column-major, so a warp writes 128 contiguous bytes),
+// and CTA 0 adds the partials in rank order, rounds once to fp16, transposes the tile through shared
+// memory and stores rows of 256 contiguous bytes of out[m, n0 .. n0 + 128).
+// HBM traffic: the packed weights once (N*K/2 bytes) plus scales; activations come from L2
+// (N/128 x M x K x 2 bytes in total, whatever the split).
 #include <cuda_fp16.h>
 
 #include "btm_internal.h"
@@ -29,32 +32,6 @@
 #include "gemm_epilogue.cuh"
 
 namespace btm {
-
-namespace i4tc {
-constexpr int BN = 64;            // weight rows per CTA = UMMA N
-constexpr int BKE = 64;           // k per operand stage
-constexpr int CHUNK_K = 256;      // k per raw-weight chunk (128 bytes per row)
-constexpr int RAW_BYTES = BN * 128;
-constexpr int RAW_STAGES = 2;
-constexpr int A_STAGES = 8; // activation tiles in flight (they come from L2 with about a microsecond of latency); the
-                            // dequantised-weight ring is fed locally and stays short
-constexpr int B_STAGES = 3;
-constexpr int B_BYTES = BN * 128; // dequantised tile: 64 rows x 64 k fp16
-constexpr int THREADS = 192;
-constexpr int TMEM_COLS = 64;
-template <int BMR> // activation rows loaded per stage: 64 or 128
-struct Cfg {
-    static constexpr int A_BYTES = BMR * 128;
-    // The tensor core always reads 128 rows of A. With BMR = 64 the upper half of that read falls on the
-    // next activation tile (or, for the last one, on the B ring, which follows); it only feeds accumulator
-    // rows 64..127, which are never stored.
-    static constexpr int A_RING_BYTES = A_STAGES * A_BYTES;
-    static constexpr int B_RING_BYTES = B_STAGES * B_BYTES;
-    // The epilogue staging (16 KB) reuses the raw-weight ring, which is dead once the main loop is over.
-    static_assert(RAW_STAGES * RAW_BYTES >= EPI_SMEM_BYTES / 2, "epilogue staging must fit in the raw ring");
-    static constexpr int SMEM_BYTES = RAW_STAGES * RAW_BYTES + A_RING_BYTES + B_RING_BYTES + 1024; // + BN*G*2 bytes of scales at run time
-};
-} // namespace i4tc
 
 __device__ __forceinline__ uint32_t i4_and_xor(uint32_t a, uint32_t b, uint32_t c)
 {
@@ -82,190 +59,327 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t x, __half2 s2)
                       *reinterpret_cast<uint32_t *>(&r3));
 }
 
-template <int BMR>
+namespace i4tc {
+constexpr int BW = 128;            // weight rows per CTA = UMMA M
+constexpr int BKE = 64;            // k per operand stage
+constexpr int UNIT_K = 128;        // k per raw-weight unit (64 bytes per row)
+constexpr int RAW_BYTES = BW * 64; // 8 KB
+constexpr int W_BYTES = BW * 128;  // dequantised tile: 128 rows x 64 k fp16
+constexpr int W_STAGES = 3;
+constexpr int THREADS = 352;       // warp 0 weight TMA, 1 MMA, 2 activation TMA, 3..10 dequantise + epilogue
+constexpr int DQ_FIRST = 96;       // first dequantising thread
+constexpr int MAX_SPLIT = 3;
+constexpr int RED_COLS = 64;       // accumulator columns reduced per round
+constexpr int RED_FLOATS = RED_COLS * BW;
+constexpr int RED_BYTES = RED_FLOATS * 4; // one CTA's partials for one round (32 KB)
+constexpr int OUT_TILE_OFF = (MAX_SPLIT - 1) * RED_BYTES; // fp16 [64 m][128 n] staging behind the partials
+template <int MB> // activation rows per pass: 64 or 128 (= UMMA N = accumulator columns)
+struct Cfg {
+    static constexpr int RAW_STAGES = MB == 64 ? 4 : 3;
+    static constexpr int ACT_STAGES = MB == 64 ? 3 : 2;
+    static constexpr int ACT_BYTES = MB * 128;
+    static constexpr int RING_BYTES = W_STAGES * W_BYTES + ACT_STAGES * ACT_BYTES + RAW_STAGES * RAW_BYTES;
+    // After the main loop the rings are dead and hold the other CTAs' partial accumulators and the output tile.
+    static_assert(OUT_TILE_OFF + RED_COLS * BW * 2 <= RING_BYTES, "reduction buffers must fit in the rings");
+    static constexpr int SMEM_BYTES = RING_BYTES + 1024; // + BW * groups-in-slice * 2 bytes of scales at run time
+};
+constexpr int SCALE_SMEM_MAX = 6144;
+} // namespace i4tc
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_ctaid_x()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+// All threads of all CTAs of the cluster; release/acquire, so shared-memory stores made before it (also
+// into another CTA's shared memory) are visible after it.
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_b32(uint32_t addr, uint32_t bits)
+{
+    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(addr), "r"(bits) : "memory");
+}
+
+template <int MB>
 __global__ void __launch_bounds__(i4tc::THREADS, 2)
-int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ CUtensorMap tmW,
-                    const __grid_constant__ StoreMaps cmaps, const GemmParams p, const __half *__restrict__ scales, int group,
-                    int m_base)
+int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ CUtensorMap tmW, const GemmParams p,
+                    const __half *__restrict__ scales, int group, int m_base)
 {
     using namespace i4tc;
-    using C = Cfg<BMR>;
+    using C = Cfg<MB>;
+    constexpr int RAW_STAGES = C::RAW_STAGES, ACT_STAGES = C::ACT_STAGES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_raw_full[RAW_STAGES], bar_raw_empty[RAW_STAGES];
-    __shared__ __align__(8) uint64_t bar_a_full[A_STAGES], bar_a_empty[A_STAGES], bar_b_full[B_STAGES], bar_b_empty[B_STAGES];
+    __shared__ __align__(8) uint64_t bar_act_full[ACT_STAGES], bar_act_empty[ACT_STAGES], bar_w_full[W_STAGES], bar_w_empty[W_STAGES];
     __shared__ __align__(8) uint64_t bar_acc_full;
     __shared__ uint32_t tmem_base_holder;
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t raw_base = smem_base;
-    const uint32_t a_ring = smem_base + RAW_STAGES * RAW_BYTES;
-    const uint32_t b_ring = a_ring + C::A_RING_BYTES;
-    const uint32_t epi_base = raw_base; // reused after the main loop
-    // scales of the CTA's 64 rows, [row][G] fp16, behind the epilogue staging area
-    __half *sc_s = reinterpret_cast<__half *>(smem_raw + (b_ring + C::B_RING_BYTES - smem_u32(smem_raw)));
-    const int n0 = blockIdx.x * BN;
-    const int nkb = (p.K + BKE - 1) / BKE;
-    const int nchunks = (p.K + CHUNK_K - 1) / CHUNK_K;
-    // Every CTA walks K starting at a different chunk: all CTAs read the same activations, and in lock step
-    // they would all ask the same L2 lines at the same moment (measured: 2 TB/s instead of the L2 rate).
-    const int c_first = (int)(blockIdx.x % (unsigned)nchunks);
+    uint8_t *smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t w_ring = smem_base;
+    const uint32_t act_ring = w_ring + W_STAGES * W_BYTES;
+    const uint32_t raw_ring = act_ring + ACT_STAGES * C::ACT_BYTES;
+    __half *sc_s = reinterpret_cast<__half *>(smem_al + C::RING_BYTES);
 
-    if (threadIdx.x == 0) {
+    const uint32_t crank = cluster_ctarank(), csize = cluster_nctarank();
+    const int tile = (int)cluster_ctaid_x();
+    const int n0 = tile * BW;
+    // This CTA's K slice, in 128-k units; every CTA starts its walk at a different unit of the slice: CTAs of
+    // the same rank read the same activations and in lock step would all ask the same L2 lines at once.
+    const int units = p.K / UNIT_K;
+    const int u0 = (int)((long long)units * crank / csize), u1 = (int)((long long)units * (crank + 1) / csize);
+    const int n_units = u1 - u0;
+    const int u_first = n_units > 0 ? tile % n_units : 0;
+    const int g_first = (u0 * UNIT_K) / group;
+    const int g_cnt = n_units > 0 ? (u1 * UNIT_K - 1) / group - g_first + 1 : 0;
+    // i-th unit of this CTA's walk
+    auto unit_at = [&](int i) {
+        int u = u_first + i;
+        if (u >= n_units) u -= n_units;
+        return u + u0;
+    };
+
+    if (warp == 0 && lane == 0) {
         abort_flag = 0;
         for (int i = 0; i < RAW_STAGES; ++i) {
             mbar_init(smem_u32(&bar_raw_full[i]), 1);
-            mbar_init(smem_u32(&bar_raw_empty[i]), 4);
+            mbar_init(smem_u32(&bar_raw_empty[i]), 8);
         }
-        for (int i = 0; i < A_STAGES; ++i) {
-            mbar_init(smem_u32(&bar_a_full[i]), 1);
-            mbar_init(smem_u32(&bar_a_empty[i]), 1);
+        for (int i = 0; i < ACT_STAGES; ++i) {
+            mbar_init(smem_u32(&bar_act_full[i]), 1);
+            mbar_init(smem_u32(&bar_act_empty[i]), 1);
         }
-        for (int i = 0; i < B_STAGES; ++i) {
-            mbar_init(smem_u32(&bar_b_full[i]), 4);
-            mbar_init(smem_u32(&bar_b_empty[i]), 1);
+        for (int i = 0; i < W_STAGES; ++i) {
+            mbar_init(smem_u32(&bar_w_full[i]), 4);
+            mbar_init(smem_u32(&bar_w_empty[i]), 1);
         }
         mbar_init(smem_u32(&bar_acc_full), 1);
         fence_mbar_init();
-        prefetch_tmap(&tmAct);
-        prefetch_tmap(&tmW);
+        // The first weight units are requested before anything else in the CTA is set up: they come from HBM
+        // and everything downstream waits for them.
+        for (int i = 0; i < RAW_STAGES && i < n_units; ++i) {
+            mbar_expect_tx(smem_u32(&bar_raw_full[i]), RAW_BYTES);
+            tma_load_3d(raw_ring + i * RAW_BYTES, &tmW, unit_at(i) * (UNIT_K / 2), n0, 0, smem_u32(&bar_raw_full[i]));
+        }
     }
     if (warp == 1) {
-        tmem_alloc<1>(smem_u32(&tmem_base_holder), TMEM_COLS);
+        tmem_alloc<1>(smem_u32(&tmem_base_holder), MB);
         tmem_relinquish<1>();
     }
+    if (warp == 2 && lane == 0) prefetch_tmap(&tmAct);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_holder;
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ TMA producer: packed weights
         if (lane == 0) {
-            int rs = 0, os = 0;
-            uint32_t rphase = 0, ophase = 0;
-            bool ok = true;
-            for (int ci = 0; ok && ci < nchunks; ++ci) {
-                const int c = (c_first + ci) % nchunks;
+            int rs = 0;
+            uint32_t rphase = 1; // the ring was filled once during set-up
+            for (int i = RAW_STAGES; i < n_units; ++i) {
                 if (!mbar_wait(smem_u32(&bar_raw_empty[rs]), rphase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) break;
                 mbar_expect_tx(smem_u32(&bar_raw_full[rs]), RAW_BYTES);
-                tma_load_3d(raw_base + rs * RAW_BYTES, &tmW, c * (CHUNK_K / 2), n0, 0, smem_u32(&bar_raw_full[rs]));
+                tma_load_3d(raw_ring + rs * RAW_BYTES, &tmW, unit_at(i) * (UNIT_K / 2), n0, 0, smem_u32(&bar_raw_full[rs]));
                 if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1u; }
-                const int kb_end = min(nkb, (c + 1) * (CHUNK_K / BKE));
-                for (int kb = c * (CHUNK_K / BKE); kb < kb_end; ++kb) {
-                    if (!mbar_wait(smem_u32(&bar_a_empty[os]), ophase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------ TMA producer: activation tiles
+        if (lane == 0) {
+            int as = 0;
+            uint32_t aphase = 0;
+            bool ok = true;
+            for (int i = 0; ok && i < n_units; ++i) {
+                const int u = unit_at(i);
+                for (int q = 0; q < UNIT_K / BKE; ++q) {
+                    if (!mbar_wait(smem_u32(&bar_act_empty[as]), aphase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(smem_u32(&bar_a_full[os]), C::A_BYTES);
-                    tma_load_3d(a_ring + os * C::A_BYTES, &tmAct, kb * BKE, m_base, 0, smem_u32(&bar_a_full[os]));
-                    if (++os == A_STAGES) { os = 0; ophase ^= 1u; }
+                    mbar_expect_tx(smem_u32(&bar_act_full[as]), C::ACT_BYTES);
+                    tma_load_3d(act_ring + as * C::ACT_BYTES, &tmAct, (u * 2 + q) * BKE, m_base, 0, smem_u32(&bar_act_full[as]));
+                    if (++as == ACT_STAGES) { as = 0; aphase ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(0u /*F16*/, false, false, 128, BN);
-            int os = 0, bs = 0;
-            uint32_t ophase = 0, bphase = 0;
+            constexpr uint32_t idesc = make_idesc(0u /*F16*/, false, false, BW, MB);
+            int as = 0, ws = 0;
+            uint32_t aphase = 0, wphase = 0;
             bool ok = true;
-            bool first = true;
-            for (int ci = 0; ok && ci < nchunks; ++ci) {
-                const int c = (c_first + ci) % nchunks;
-                const int kb_end = min(nkb, (c + 1) * (CHUNK_K / BKE));
-                for (int kb = c * (CHUNK_K / BKE); kb < kb_end; ++kb) {
-                    if (!mbar_wait_short(smem_u32(&bar_a_full[os]), ophase, &abort_flag, p.status, WAIT_MMA_FULL) ||
-                        !mbar_wait_short(smem_u32(&bar_b_full[bs]), bphase, &abort_flag, p.status, WAIT_MMA_FULL)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t a0 = a_ring + os * C::A_BYTES, b0 = b_ring + bs * B_BYTES;
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t ad = make_smem_desc_sw128(a0 + ks * 32, 16, 1024);
-                        const uint64_t bd = make_smem_desc_sw128(b0 + ks * 32, 16, 1024);
-                        umma<1, false>(tmem_base, ad, bd, idesc, first ? 0u : 1u);
-                        first = false;
-                    }
-                    umma_commit(smem_u32(&bar_a_empty[os])); // both tiles are free once these MMAs have read them
-                    umma_commit(smem_u32(&bar_b_empty[bs]));
-                    if (++os == A_STAGES) { os = 0; ophase ^= 1u; }
-                    if (++bs == B_STAGES) { bs = 0; bphase ^= 1u; }
+            for (int i = 0; ok && i < n_units * (UNIT_K / BKE); ++i) {
+                if (!mbar_wait_short(smem_u32(&bar_act_full[as]), aphase, &abort_flag, p.status, WAIT_MMA_FULL) ||
+                    !mbar_wait_short(smem_u32(&bar_w_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL)) {
+                    ok = false;
+                    break;
                 }
+                tc_fence_after();
+                const uint32_t w0 = w_ring + ws * W_BYTES, a0 = act_ring + as * C::ACT_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint64_t wd = make_smem_desc_sw128(w0 + ks * 32, 16, 1024);
+                    const uint64_t ad = make_smem_desc_sw128(a0 + ks * 32, 16, 1024);
+                    umma<1, false>(tmem_base, wd, ad, idesc, (i | ks) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&bar_w_empty[ws])); // both tiles are free once these MMAs have read them
+                umma_commit(smem_u32(&bar_act_empty[as]));
+                if (++as == ACT_STAGES) { as = 0; aphase ^= 1u; }
+                if (++ws == W_STAGES) { ws = 0; wphase ^= 1u; }
             }
             if (ok) umma_commit(smem_u32(&bar_acc_full));
         }
     } else {
-        // ------------------------------------------------------------ dequantise (warps 2..5), then epilogue
-        const int dq = threadIdx.x - 64;     // 0..127
-        const int row = dq >> 1, hsel = dq & 1; // weight row in the tile, which 32-k half of the block
+        // ------------------------------------------------------------ dequantise (warps 3..10)
+        // Thread = (weight row, which 64-k block of the unit): warps 3..6 fill the unit's first operand stage,
+        // warps 7..10 the second, at the same time.
+        const int dq = threadIdx.x - DQ_FIRST; // 0..255
+        const int q = dq >> 7, row = dq & 127;
+        // The eight warps fetch the slice's scales together, right away (a load issued once the weight
+        // stream is queued would come back last), and meet on a named barrier of their own.
         const int G = p.K / group;
-        // The four dequantising warps fetch the tile's scales together, right away (a load issued once the
-        // weight stream is queued would come back last), and meet on a named barrier of their own.
-        for (int i = dq; i < BN * G; i += 128) sc_s[i] = __ldg(scales + min((size_t)n0 * G + i, (size_t)p.N * G - 1));
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const __half *srow = sc_s + row * G;
-        const int gdiv = group / BKE; // k-blocks per scale group (group is a multiple of 64)
-        const uint32_t swz = (uint32_t)(row & 7);
-        int rs = 0, os = 0;
-        uint32_t rphase = 0, ophase = 0;
-        bool ok = true;
-        for (int ci = 0; ok && ci < nchunks; ++ci) {
-            const int c = (c_first + ci) % nchunks;
-            ok = mbar_wait_short_warp(smem_u32(&bar_raw_full[rs]), rphase, &abort_flag, p.status, WAIT_EPI_STAGE);
-            if (!ok) break;
-            const uint32_t raw_row = raw_base + rs * RAW_BYTES + (uint32_t)row * 128u;
-            const int kb_first = c * (CHUNK_K / BKE);
-            const int nq = min(nkb, kb_first + CHUNK_K / BKE) - kb_first; // k-blocks in this chunk (1..4)
-            // All packed words of the chunk are fetched and dequantised first (four independent instruction
-            // streams for the scheduler to interleave); the stage hand-offs follow.
-            uint4 d[CHUNK_K / BKE][4];
-#pragma unroll
-            for (int q = 0; q < CHUNK_K / BKE; ++q) {
-                if (q < nq) {
-                    uint4 pw; // packed 16 bytes = 32 nibbles: k = (kb_first + q)*64 + hsel*32 .. +32 of this row
-                    const uint32_t src = raw_row + ((((uint32_t)(q * 2 + hsel)) ^ swz) << 4);
-                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(pw.x), "=r"(pw.y), "=r"(pw.z), "=r"(pw.w) : "r"(src));
-                    const int kb = kb_first + q;
-                    const __half2 s2 = __half2half2(srow[gdiv == 2 ? (kb >> 1) : (gdiv == 1 ? kb : kb / gdiv)]);
-                    d[q][0] = dequant_word(pw.x, s2);
-                    d[q][1] = dequant_word(pw.y, s2);
-                    d[q][2] = dequant_word(pw.z, s2);
-                    d[q][3] = dequant_word(pw.w, s2);
-                }
-            }
-            // The raw chunk is in registers now: hand the buffer back before the (possibly waiting) stores.
+        for (int i = dq; i < BW * g_cnt; i += 256) {
+            const int r = i / g_cnt, g = i - r * g_cnt;
+            sc_s[i] = __ldg(scales + (size_t)min(n0 + r, p.N - 1) * G + g_first + g);
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const __half *srow = sc_s + row * g_cnt - g_first;
+        const uint32_t xs = (uint32_t)((row >> 1) & 3), swz = (uint32_t)(row & 7);
+        const uint32_t raw_row0 = raw_ring + (uint32_t)row * 64u;
+        const uint32_t c0 = ((uint32_t)(2 * q) ^ xs) << 4, c1 = ((uint32_t)(2 * q + 1) ^ xs) << 4;
+        int rs = 0, ws = q; // block ordinal b = 2 i + q uses operand stage b % 3
+        uint32_t rphase = 0, wphase = 0;
+        bool ok = n_units > 0 && mbar_wait_short_warp(smem_u32(&bar_raw_full[0]), 0u, &abort_flag, p.status, WAIT_EPI_STAGE);
+        uint4 pa, pb; // 32 packed bytes = 64 nibbles of this row: k = u*128 + q*64 .. +64
+        if (ok) {
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(pa.x), "=r"(pa.y), "=r"(pa.z), "=r"(pa.w) : "r"(raw_row0 + c0));
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(pb.x), "=r"(pb.y), "=r"(pb.z), "=r"(pb.w) : "r"(raw_row0 + c1));
+        }
+        for (int i = 0; ok && i < n_units; ++i) {
+            const int u = unit_at(i);
+            const __half2 s2 = __half2half2(srow[((u * 2 + q) * BKE) / group]);
+            uint4 d[8];
+            d[0] = dequant_word(pa.x, s2);
+            d[1] = dequant_word(pa.y, s2);
+            d[2] = dequant_word(pa.z, s2);
+            d[3] = dequant_word(pa.w, s2);
+            d[4] = dequant_word(pb.x, s2);
+            d[5] = dequant_word(pb.y, s2);
+            d[6] = dequant_word(pb.z, s2);
+            d[7] = dequant_word(pb.w, s2);
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_raw_empty[rs]));
+            if (lane == 0) mbar_arrive(smem_u32(&bar_raw_empty[rs])); // this warp's part of the unit is in registers
+            if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1u; }
+            if (i + 1 < n_units) { // the next unit's packed words are fetched before this one's stores
+                ok = mbar_wait_short_warp(smem_u32(&bar_raw_full[rs]), rphase, &abort_flag, p.status, WAIT_EPI_STAGE);
+                if (!ok) break;
+                const uint32_t rr = raw_row0 + rs * RAW_BYTES;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(pa.x), "=r"(pa.y), "=r"(pa.z), "=r"(pa.w) : "r"(rr + c0));
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(pb.x), "=r"(pb.y), "=r"(pb.z), "=r"(pb.w) : "r"(rr + c1));
+            }
+            ok = mbar_wait_short_warp(smem_u32(&bar_w_empty[ws]), wphase ^ 1u, &abort_flag, p.status, WAIT_EPI_STAGE);
+            if (!ok) break;
+            const uint32_t wrow = w_ring + ws * W_BYTES + (uint32_t)row * 128u;
 #pragma unroll
-            for (int q = 0; q < CHUNK_K / BKE; ++q) {
-                if (q < nq) {
-                    ok = mbar_wait_short_warp(smem_u32(&bar_b_empty[os]), ophase ^ 1u, &abort_flag, p.status, WAIT_EPI_STAGE);
-                    if (!ok) break;
-                    const uint32_t brow = b_ring + os * B_BYTES + (uint32_t)row * 128u;
+            for (int j = 0; j < 8; ++j) st_shared_v4(wrow + ((((uint32_t)j) ^ swz) << 4), d[j].x, d[j].y, d[j].z, d[j].w);
+            fence_proxy_async_smem(); // generic-proxy writes -> visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_w_full[ws]));
+            ws += 2; // two blocks further on: stage (b + 2) % 3, parity flips when the ordinal passes a multiple of 3
+            if (ws >= W_STAGES) { ws -= W_STAGES; wphase ^= 1u; }
+        }
+        if (ok) mbar_wait_warp(smem_u32(&bar_acc_full), 0u, &abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+        tc_fence_after();
+    }
+
+    // ---------------------------------------------------------------- split-K reduction and output
+    // Every thread of every CTA of the cluster passes the same cluster barriers, whatever happened above.
+    __syncthreads();    // this CTA's rings are dead: its tensor-core and TMA traffic is over
+    const bool acc_ok = abort_flag == 0; // the same answer in every thread of the CTA
+    cluster_sync_all(); // ... in every CTA of the cluster, so CTA 0's rings may now be overwritten
+    const bool epi = warp >= 3;
+    const int quad = warp & 3;                 // the tensor-memory lanes this warp may read
+    const int erow = quad * 32 + lane;         // accumulator lane = weight row of the tile
+    const int chalf = (warp - 3) >> 2;         // which 32 of a round's 64 columns
+    const uint32_t red0 = map_to_cta(smem_base, 0);
+    const float *red = reinterpret_cast<const float *>(smem_al);
+    uint16_t *tile_out = reinterpret_cast<uint16_t *>(smem_al + OUT_TILE_OFF);
+    uint16_t *out = reinterpret_cast<uint16_t *>(p.C[0]);
+    const bool vec_store = (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+#pragma unroll 1
+    for (int h = 0; h < MB / RED_COLS; ++h) {
+        uint32_t v[32];
+        if (epi) {
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * RED_COLS + chalf * 32), v);
+            tmem_ld_wait();
+            if (crank != 0 && acc_ok) {
+                const uint32_t dst = red0 + (crank - 1) * RED_BYTES + (uint32_t)(chalf * 32 * BW + erow) * 4u;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        st_shared_v4(brow + ((((uint32_t)(hsel * 4 + j)) ^ swz) << 4), d[q][j].x, d[q][j].y, d[q][j].z, d[q][j].w);
-                    fence_proxy_async_smem(); // generic-proxy writes -> visible to the tensor core's reads
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bar_b_full[os]));
-                    if (++os == B_STAGES) { os = 0; ophase ^= 1u; }
+                for (int c = 0; c < 32; ++c) st_cluster_b32(dst + (uint32_t)c * (BW * 4), v[c]);
+            }
+        }
+        cluster_sync_all(); // partials of this round are in CTA 0's shared memory
+        if (epi && crank == 0 && acc_ok) {
+            float acc[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) acc[c] = __uint_as_float(v[c]);
+#pragma unroll
+            for (int r = 1; r < MAX_SPLIT; ++r) {
+                if (r < (int)csize) {
+                    const float *src = red + (r - 1) * RED_FLOATS + chalf * 32 * BW + erow;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) acc[c] += src[c * BW];
                 }
             }
-            if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1u; }
+            // fp16 tile [64 m][128 n] in shared memory, then rows of 256 contiguous bytes to global memory
+#pragma unroll
+            for (int c = 0; c < 32; ++c) tile_out[(chalf * 32 + c) * BW + erow] = __half_as_ushort(__float2half_rn(acc[c]));
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const int t = threadIdx.x - DQ_FIRST;
+            const int chunk = t & 15, n = n0 + chunk * 8;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int mt = (t >> 4) + 16 * k, m = m_base + h * RED_COLS + mt;
+                if (m < p.M && n < p.N) {
+                    const uint4 val = *reinterpret_cast<const uint4 *>(tile_out + mt * BW + chunk * 8);
+                    uint16_t *dst = out + (long long)m * p.ldc + n;
+                    if (vec_store && n + 8 <= p.N) {
+                        *reinterpret_cast<uint4 *>(dst) = val;
+                    } else {
+                        const uint32_t w[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (n + e < p.N) dst[e] = (uint16_t)((e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xFFFFu));
+                    }
+                }
+            }
         }
-        if (ok && mbar_wait_warp(smem_u32(&bar_acc_full), 0u, &abort_flag, p.status, WAIT_EPI_TMEM_FULL)) {
-            tc_fence_after();
-            const int quad = warp & 3;
-            uint32_t epi_tiles = 0;
-            // One staging tile per warp (64 output columns = one tile), carved from the epilogue area.
-            epilogue_band<BTM_F16>(p, cmaps, tmem_base + ((uint32_t)(quad * 32) << 16), m_base + quad * 32, n0, BN, 0,
-                                   epi_base + (uint32_t)quad * EPI_TILE_BYTES, epi_tiles, lane);
-            epilogue_drain(lane);
-        }
+        if (h + 1 < MB / RED_COLS) cluster_sync_all(); // CTA 0 has consumed the round: the buffers may be rewritten
     }
 
     tc_fence_before();
@@ -278,31 +392,42 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+        tmem_dealloc<1>(tmem_base, MB);
     }
 }
 
 int configure_int4_tc_kernels()
 {
-    cudaError_t e = cudaFuncSetAttribute(int4_gemm_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, i4tc::Cfg<64>::SMEM_BYTES + 8192);
+    using namespace i4tc;
+    cudaError_t e = cudaFuncSetAttribute(int4_gemm_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::SMEM_BYTES + SCALE_SMEM_MAX);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(int4_gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, i4tc::Cfg<128>::SMEM_BYTES + 8192);
+        e = cudaFuncSetAttribute(int4_gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::SMEM_BYTES + SCALE_SMEM_MAX);
     return check_cuda(e, "cudaFuncSetAttribute(int4_gemm_tc)");
 }
 
-// Preconditions (checked by the caller): K % 128 == 0, group % 64 == 0, act / w / out 16-byte aligned,
-// N % 8 == 0 (output pitch), M > 0.
+// Preconditions (checked by the caller): K % 128 == 0, group % 64 == 0, K % group == 0, act / w / out
+// 16-byte aligned, M > 0. Returns BTM_ERR_UNSUPPORTED (nothing launched) when the scales of one K slice do
+// not fit the shared memory set aside for them; the caller then takes the general kernel.
 int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const void *act, const void *w, const void *scales, void *out,
-                        int *status)
+                        int *status, int sm_count)
 {
     using namespace i4tc;
+    const int units = K / UNIT_K;
+    const int tiles = (N + BW - 1) / BW;
+    // K split: as many CTAs per weight tile as the machine holds at two CTAs per SM.
+    int split = (2 * sm_count) / tiles;
+    split = split < 1 ? 1 : split > MAX_SPLIT ? MAX_SPLIT : split;
+    if (split > units) split = units;
+    const int groups_per_slice = ((units + split - 1) / split * UNIT_K + group - 1) / group + 1;
+    const size_t sc_bytes = (size_t)BW * groups_per_slice * 2;
+    if (sc_bytes > SCALE_SMEM_MAX) return BTM_ERR_UNSUPPORTED;
     CUtensorMap tmAct, tmW;
-    int rc = encode_tmap_3d(&tmW, BTM_U8, w, (uint64_t)K / 2, (uint64_t)N, 1, (uint64_t)K / 2, (uint64_t)K / 2, 128, BN);
+    int rc = encode_tmap_3d(&tmW, BTM_U8, w, (uint64_t)K / 2, (uint64_t)N, 1, (uint64_t)K / 2, (uint64_t)K / 2, 64, BW, 2 /*64-byte swizzle*/);
     if (rc) return rc;
     for (int m_base = 0; m_base < M; m_base += 128) {
         const int rows = M - m_base < 128 ? M - m_base : 128;
-        const int bmr = rows <= 64 ? 64 : 128;
-        rc = encode_tmap_3d(&tmAct, BTM_F16, act, (uint64_t)K, (uint64_t)M, 1, (uint64_t)K * 2, (uint64_t)K * 2, 64, (uint32_t)bmr);
+        const int mb = rows <= 64 ? 64 : 128;
+        rc = encode_tmap_3d(&tmAct, BTM_F16, act, (uint64_t)K, (uint64_t)M, 1, (uint64_t)K * 2, (uint64_t)K * 2, 64, (uint32_t)mb);
         if (rc) return rc;
         GemmParams p;
         memset(&p, 0, sizeof(p));
@@ -313,18 +438,28 @@ int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const v
         p.ndst = 1;
         p.C[0] = out;
         p.ldc = N;
-        p.c_vec_ok = 1;
         p.status = status;
-        StoreMaps cm;
-        rc = encode_store_maps(&cm, BTM_F16, p);
-        if (rc) return rc;
-        const unsigned grid = (unsigned)((N + BN - 1) / BN);
-        const size_t sc_bytes = (size_t)BN * (K / group) * 2;
-        if (bmr == 64)
-            int4_gemm_tc_kernel<64><<<grid, THREADS, Cfg<64>::SMEM_BYTES + sc_bytes, st>>>(tmAct, tmW, cm, p, (const __half *)scales, group, m_base);
-        else
-            int4_gemm_tc_kernel<128><<<grid, THREADS, Cfg<128>::SMEM_BYTES + sc_bytes, st>>>(tmAct, tmW, cm, p, (const __half *)scales, group, m_base);
-        rc = check_cuda(cudaGetLastError(), "int4 tensor-core matmul launch");
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)(tiles * split), 1, 1);
+        cfg.blockDim = dim3(THREADS, 1, 1);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)split;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e;
+        if (mb == 64) {
+            cfg.dynamicSmemBytes = Cfg<64>::SMEM_BYTES + sc_bytes;
+            e = cudaLaunchKernelEx(&cfg, int4_gemm_tc_kernel<64>, tmAct, tmW, p, (const __half *)scales, group, m_base);
+        } else {
+            cfg.dynamicSmemBytes = Cfg<128>::SMEM_BYTES + sc_bytes;
+            e = cudaLaunchKernelEx(&cfg, int4_gemm_tc_kernel<128>, tmAct, tmW, p, (const __half *)scales, group, m_base);
+        }
+        rc = check_cuda(e, "int4 tensor-core matmul launch");
         if (rc) return rc;
     }
     return BTM_OK;

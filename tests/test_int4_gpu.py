@@ -99,7 +99,8 @@ def test_bad_arguments(btm):
 
 
 @pytest.mark.parametrize("path", ["tensor_core", "mma"])
-@pytest.mark.parametrize("case", [(16, 128, 256, 128), (64, 1088, 1024, 128), (100, 200, 512, 64), (129, 72, 1024, 256), (40, 64, 4096, 128)])
+@pytest.mark.parametrize("case", [(16, 128, 256, 128), (64, 1088, 1024, 128), (100, 200, 512, 64), (129, 72, 1024, 256), (40, 64, 4096, 128),
+                                  (16, 19200, 256, 128), (24, 12800, 512, 128), (20, 33, 384, 128)])
 def test_more_than_eight_rows_both_paths(btm, oracle, case, path, monkeypatch):
     # M > 8 runs on tcgen05 (weights dequantised into shared memory) unless pinned to the mma.sync kernel.
     M, N, K, group = case
