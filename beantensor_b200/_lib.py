@@ -23,6 +23,7 @@ SIGNATURES = {
     "btm_init": (_i, [_i]),
     "btm_check_device_status": (_i, [_i, _vp]),
     "btm_gemm": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "btm_gemm_bias_act": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i, _vp, _i64]),
     "btm_gemm_bt": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
     "btm_gemm_f32_workspace_bytes": (_sz, [_i, _i, _i]),
     "btm_gemm_f32_ws": (_i, [_i, _vp, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _sz]),

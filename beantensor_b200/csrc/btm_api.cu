@@ -144,6 +144,8 @@ struct GemmCall {
     void *C[kMaxDst];
     int ndst;
     long long ldc, strideC, col0;
+    const void *bias; // optional, one value per column of this launch's N
+    int act;          // 0 none, 1 ReLU
 };
 
 static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
@@ -153,7 +155,7 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
     if (!tc) {
         for (int d = 0; d < c.ndst; ++d) {
             int rc = launch_gemm_simt(c.dtype, st, c.batch, c.M, c.N, c.K, c.A, c.lda, c.strideA, c.B, c.ldb, c.strideB,
-                                      (char *)c.C[d] + c.col0 * (long long)es, c.ldc, c.strideC);
+                                      (char *)c.C[d] + c.col0 * (long long)es, c.ldc, c.strideC, c.bias, c.act);
             if (rc) return rc;
         }
         return BTM_OK;
@@ -184,6 +186,8 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
     p.col0 = c.col0;
     p.c_vec_ok = vec ? 1 : 0;
     p.status = ds->status;
+    p.bias = c.bias;
+    p.act = c.act;
     if (c.ndst > 1) {
         // Peer stores of a tile are spread over part of the next tile's main loop instead of leaving the
         // SM as one burst. Unit: SM cycles per 64-deep k-block (a k-block of a 256 x 256 pair tile takes
@@ -219,7 +223,7 @@ static int run_f32(DeviceState *ds, cudaStream_t st, const GemmCall &c, void *ws
     const size_t a_plane = (size_t)c.M * Kp, b_plane = (size_t)c.N * Kp;
     const size_t need = (2 * a_plane + 2 * b_plane) * sizeof(float);
     if (c.K == 0 || c.M == 0 || c.N == 0)
-        return launch_gemm_simt(BTM_F32, st, 1, c.M, c.N, c.K, c.A, c.lda, 0, c.B, c.ldb, 0, c.C[0], c.ldc, 0);
+        return launch_gemm_simt(BTM_F32, st, 1, c.M, c.N, c.K, c.A, c.lda, 0, c.B, c.ldb, 0, c.C[0], c.ldc, 0, c.bias, c.act);
     if (ws_bytes < need) return set_error(BTM_ERR_INVALID, "fp32 matmul: workspace of %zu bytes is smaller than the %zu needed", ws_bytes, need);
     float *a_hi = (float *)ws, *a_lo = a_hi + a_plane, *b_hi = a_lo + a_plane, *b_lo = b_hi + b_plane;
     int rc = launch_split_tf32_pair(st, (const float *)c.A, c.lda, c.M, c.K, a_hi, a_lo, (const float *)c.B, c.ldb, c.N, b_hi, b_lo, Kp);
@@ -245,6 +249,8 @@ static int run_f32(DeviceState *ds, cudaStream_t st, const GemmCall &c, void *ws
     p.ldc = c.ldc;
     p.c_vec_ok = (aligned16(c.C[0]) && (c.ldc * 4) % 16 == 0) ? 1 : 0;
     p.status = ds->status;
+    p.bias = c.bias;
+    p.act = c.act;
     StoreMaps cm;
     rc = encode_store_maps(&cm, BTM_F32, p);
     if (rc) return rc;
@@ -309,8 +315,8 @@ int btm_check_device_status(int device, void *stream)
     return BTM_OK;
 }
 
-int btm_gemm(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B, int64_t ldb,
-             void *C, int64_t ldc)
+static int gemm_entry(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B, int64_t ldb,
+                      void *C, int64_t ldc, const void *bias, int act)
 {
     int rc = check_gemm_args(dtype, M, N, K, A, lda, B, ldb, C, ldc);
     if (rc) return rc;
@@ -323,6 +329,7 @@ int btm_gemm(int device, void *stream, int dtype, int M, int N, int K, const voi
     c.dtype = dtype; c.batch = 1; c.M = M; c.N = N; c.K = K;
     c.A = A; c.B = B; c.lda = lda; c.ldb = ldb;
     c.C[0] = C; c.ndst = 1; c.ldc = ldc;
+    c.bias = bias; c.act = act;
     if (dtype != BTM_F32) return run_16bit(ds, st, c);
     const size_t need = btm_gemm_f32_workspace_bytes(M, N, K);
     {
@@ -340,6 +347,19 @@ int btm_gemm(int device, void *stream, int dtype, int M, int N, int K, const voi
         }
     }
     return run_f32(ds, st, c, ds->ws, ds->ws_bytes);
+}
+
+int btm_gemm(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B, int64_t ldb,
+             void *C, int64_t ldc)
+{
+    return gemm_entry(device, stream, dtype, M, N, K, A, lda, B, ldb, C, ldc, nullptr, BTM_ACT_NONE);
+}
+
+int btm_gemm_bias_act(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B,
+                      int64_t ldb, const void *bias, int act, void *C, int64_t ldc)
+{
+    if (act != BTM_ACT_NONE && act != BTM_ACT_RELU) return set_error(BTM_ERR_INVALID, "matmul: unknown activation %d", act);
+    return gemm_entry(device, stream, dtype, M, N, K, A, lda, B, ldb, C, ldc, bias, act);
 }
 
 size_t btm_gemm_f32_workspace_bytes(int M, int N, int K)

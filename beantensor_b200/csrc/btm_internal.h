@@ -25,6 +25,8 @@ struct GemmParams {
     long long strideC; // elements between products
     long long col0;    // first output column of this launch inside C
     int pace_cycles;   // >0: peer stores of one tile are spread over this many SM cycles (several destinations only)
+    const void *bias;  // optional: one value per output column (same dtype as C), added to the fp32 accumulator before rounding
+    int act;           // 0 none, 1 ReLU (after the bias)
     int c_vec_ok;      // 16-byte vector stores into C are legal
     int *status;       // device status word (bounded waits report here)
 };
@@ -56,9 +58,10 @@ int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &
                    const GemmParams &p, int force_bn);
 int launch_gemm_tc_bt(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
                       const GemmParams &p, int bn);
+// bias / act: see GemmParams.
 int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K, const void *A, long long lda,
                      long long strideA, const void *B, long long ldb, long long strideB, void *C, long long ldc,
-                     long long strideC);
+                     long long strideC, const void *bias = nullptr, int act = 0);
 int launch_split_tf32(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
                       float *dst_lo, long long ld_dst);
 int launch_split_tf32_pair(cudaStream_t st, const float *A, long long lda, int M, int K, float *a_hi, float *a_lo, const float *B,

@@ -61,6 +61,27 @@ __device__ __forceinline__ void pack16(const uint32_t (&acc)[32], uint32_t (&pac
     }
 }
 
+// Fused bias and activation on 32 accumulator columns (col .. col + 31) of this lane's row: lane j fetches
+// bias[col + j] once and the values go round the warp by shuffle. Nothing is done (one uniform branch) when
+// the launch has neither.
+template <int DT>
+__device__ __forceinline__ void bias_act(const GemmParams &p, uint32_t (&v)[32], int col, int lane)
+{
+    if (p.bias == nullptr && p.act == 0) return;
+    float b = 0.0f;
+    if (p.bias != nullptr && col + lane < p.N) {
+        if constexpr (DT == BTM_F32) b = __ldg(reinterpret_cast<const float *>(p.bias) + col + lane);
+        else if constexpr (DT == BTM_F16) b = __half2float(__ldg(reinterpret_cast<const __half *>(p.bias) + col + lane));
+        else b = __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16 *>(p.bias) + col + lane));
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        float x = __uint_as_float(v[j]) + __shfl_sync(0xffffffffu, b, j);
+        if (p.act == 1) x = fmaxf(x, 0.0f);
+        v[j] = __float_as_uint(x);
+    }
+}
+
 // Per-thread stores of 32 consecutive columns of one output row (general path).
 template <int DT>
 __device__ __forceinline__ void store_row_direct(const GemmParams &p, const uint32_t (&acc)[32], long long elem_off, int ncols_valid)
@@ -115,6 +136,7 @@ __device__ __forceinline__ void epilogue_band_multi(const GemmParams &p, const S
                 uint32_t v[32], q[16];
                 tmem_ld_32x32(tmem_band + (uint32_t)(c * 128 + t * 64 + h * 32), v);
                 tmem_ld_wait();
+                bias_act<DT>(p, v, col_first + c * 128 + t * 64 + h * 32, lane);
                 pack16<DT>(v, q);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
@@ -184,6 +206,7 @@ __device__ __forceinline__ void epilogue_band(const GemmParams &p, const StoreMa
             tmem_ld_32x32(tmem_band + (uint32_t)(c * 32), v);
             tmem_ld_wait();
             const int col = col_first + c * 32;
+            bias_act<DT>(p, v, col, lane);
             const int valid = min(32, p.N - col);
             if (row < p.M && valid > 0) store_row_direct<DT>(p, v, row_off + col, valid);
         }
@@ -208,6 +231,7 @@ __device__ __forceinline__ void epilogue_band(const GemmParams &p, const StoreMa
             uint32_t v[32];
             tmem_ld_32x32(tmem_band + (uint32_t)(c * 32), v);
             tmem_ld_wait();
+            bias_act<DT>(p, v, col_first + c * 32, lane);
 #pragma unroll
             for (int j = 0; j < 8; ++j) st_shared_v4(row_addr + (((uint32_t)j ^ swz) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         } else {
@@ -216,6 +240,7 @@ __device__ __forceinline__ void epilogue_band(const GemmParams &p, const StoreMa
                 uint32_t v[32], q[16];
                 tmem_ld_32x32(tmem_band + (uint32_t)(c * 64 + h * 32), v);
                 tmem_ld_wait();
+                bias_act<DT>(p, v, col_first + c * 64 + h * 32, lane);
                 pack16<DT>(v, q);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)

@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(int M, int N, int K, con
                                                         long long lda, long long strideA,
                                                         const typename Elem<DT>::T *__restrict__ B, long long ldb,
                                                         long long strideB, typename Elem<DT>::T *__restrict__ C,
-                                                        long long ldc, long long strideC)
+                                                        long long ldc, long long strideC,
+                                                        const typename Elem<DT>::T *__restrict__ bias, int act)
 {
     constexpr int TM = 64, TN = 64, TK = 16;
     __shared__ float As[TK][TM + 1];
@@ -80,14 +81,19 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(int M, int N, int K, con
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
-            if (gn < N) Elem<DT>::store(C + (long long)gm * ldc + gn, acc[i][j]);
+            if (gn < N) {
+                float v = acc[i][j];
+                if (bias) v += Elem<DT>::load(bias + gn);
+                if (act == 1) v = fmaxf(v, 0.0f);
+                Elem<DT>::store(C + (long long)gm * ldc + gn, v);
+            }
         }
     }
 }
 
 int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K, const void *A, long long lda,
                      long long strideA, const void *B, long long ldb, long long strideB, void *C, long long ldc,
-                     long long strideC)
+                     long long strideC, const void *bias, int act)
 {
     if (M == 0 || N == 0 || batch == 0) return BTM_OK;
     const long long gy = (M + 63) / 64, gx = (N + 63) / 64;
@@ -96,15 +102,15 @@ int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K,
     switch (dtype) {
     case BTM_F32:
         gemm_simt_kernel<BTM_F32><<<grid, 256, 0, st>>>(M, N, K, (const float *)A, lda, strideA, (const float *)B, ldb, strideB,
-                                                        (float *)C, ldc, strideC);
+                                                        (float *)C, ldc, strideC, (const float *)bias, act);
         break;
     case BTM_F16:
         gemm_simt_kernel<BTM_F16><<<grid, 256, 0, st>>>(M, N, K, (const __half *)A, lda, strideA, (const __half *)B, ldb, strideB,
-                                                        (__half *)C, ldc, strideC);
+                                                        (__half *)C, ldc, strideC, (const __half *)bias, act);
         break;
     case BTM_BF16:
         gemm_simt_kernel<BTM_BF16><<<grid, 256, 0, st>>>(M, N, K, (const __nv_bfloat16 *)A, lda, strideA, (const __nv_bfloat16 *)B,
-                                                         ldb, strideB, (__nv_bfloat16 *)C, ldc, strideC);
+                                                         ldb, strideB, (__nv_bfloat16 *)C, ldc, strideC, (const __nv_bfloat16 *)bias, act);
         break;
     default:
         return set_error(BTM_ERR_UNSUPPORTED, "matmul: dtype %d is not supported", dtype);

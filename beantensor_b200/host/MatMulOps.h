@@ -58,6 +58,32 @@ inline const void *btm_base(const btm_tensor_view &t)
     return static_cast<const char *>(t.data) + t.offset * btm_dtype_size(t.dtype);
 }
 
+// out[M,N] = act(a[M,K] . b[K,N] + bias[N]). Float16/BFloat16 (fp32 accumulate) or Float32 (3xTF32).
+// `bias` may be null (none); `relu` applies max(x, 0) after the bias. The product, the reference's broadcast Add
+// (Ops/Elementwise/Add/Add.h:28) and its Relu stub (Ops/Elementwise/Relu/Relu.h) in one kernel: out is written once.
+inline void matmul_bias_act_gpu(const btm_tensor_view &a, const btm_tensor_view &b, const btm_tensor_view *bias, bool relu,
+                                btm_tensor_view &out, void *stream = nullptr)
+{
+    btm_require_gpu_rowmajor(a, 2, "matmul_gpu(a)");
+    btm_require_gpu_rowmajor(b, 2, "matmul_gpu(b)");
+    btm_require_gpu_rowmajor(out, 2, "matmul_gpu(out)");
+    if (a.dtype != b.dtype || a.dtype != out.dtype) throw std::invalid_argument("matmul_gpu: dtypes differ");
+    if (a.gpu_id != b.gpu_id || a.gpu_id != out.gpu_id) throw std::invalid_argument("matmul_gpu: tensors live on different GPUs");
+    if (a.shape[1] != b.shape[0] || out.shape[0] != a.shape[0] || out.shape[1] != b.shape[1])
+        throw std::invalid_argument("matmul_gpu: shape mismatch");
+    if (bias) {
+        btm_require_gpu_rowmajor(*bias, 1, "matmul_gpu(bias)");
+        if (bias->dtype != out.dtype || bias->gpu_id != out.gpu_id || bias->shape[0] != out.shape[1])
+            throw std::invalid_argument("matmul_gpu: bias must be a [N] tensor of the output's dtype on the output's GPU");
+    }
+    const int M = (int)a.shape[0], K = (int)a.shape[1], N = (int)b.shape[1];
+    const int64_t lda = M > 1 ? (int64_t)a.strides[0] : (K > 0 ? K : 1);
+    const int64_t ldb = K > 1 ? (int64_t)b.strides[0] : (N > 0 ? N : 1);
+    const int64_t ldc = M > 1 ? (int64_t)out.strides[0] : (N > 0 ? N : 1);
+    btm_raise(btm_gemm_bias_act(a.gpu_id, stream, a.dtype, M, N, K, btm_base(a), lda, btm_base(b), ldb, bias ? btm_base(*bias) : nullptr,
+                                relu ? BTM_ACT_RELU : BTM_ACT_NONE, const_cast<void *>(btm_base(out)), ldc));
+}
+
 // out[M,N] = a[M,K] . b[K,N]. Float16/BFloat16 (fp32 accumulate) or Float32 (3xTF32).
 inline void matmul_gpu(const btm_tensor_view &a, const btm_tensor_view &b, btm_tensor_view &out, void *stream = nullptr)
 {

@@ -50,9 +50,18 @@ def check_device_status(device: int = 0) -> None:
     raise_for_status(_lib.lib().btm_check_device_status(device, _stream()))
 
 
-def matmul_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M,N] = a[M,K] . b[K,N]; fp16/bf16 (fp32 accumulate) or fp32 (3xTF32)."""
+def matmul_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
+               relu: bool = False) -> None:
+    """out[M,N] = a[M,K] . b[K,N]; fp16/bf16 (fp32 accumulate) or fp32 (3xTF32).
+
+    With `bias` ([N], dtype of out) and/or `relu` the epilogue is fused: out = relu(a.b + bias), rounded once.
+    """
     dev = _require_gpu(a, b, out)
+    if bias is not None:
+        if not bias.is_cuda or bias.device != out.device:
+            raise ValueError("matmul_gpu: bias is not on the output's GPU")
+        if bias.dim() != 1 or bias.shape[0] != out.shape[-1] or bias.dtype != out.dtype or not bias.is_contiguous():
+            raise ValueError("matmul_gpu: bias must be a contiguous [N] tensor of the output's dtype")
     if a.dim() != 2 or b.dim() != 2 or out.dim() != 2:
         raise ValueError("matmul_gpu takes 2-D tensors")
     if a.dtype != b.dtype or a.dtype != out.dtype:
@@ -69,8 +78,13 @@ def matmul_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
     lda = a.stride(0) if M > 1 else max(K, 1)
     ldb = b.stride(0) if K > 1 else max(N, 1)
     ldc = out.stride(0) if M > 1 else max(N, 1)
-    rc = _lib.lib().btm_gemm(dev, _stream(), _DT[a.dtype], M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
-                             out.data_ptr(), ldc)
+    if bias is None and not relu:
+        rc = _lib.lib().btm_gemm(dev, _stream(), _DT[a.dtype], M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
+                                 out.data_ptr(), ldc)
+    else:
+        rc = _lib.lib().btm_gemm_bias_act(dev, _stream(), _DT[a.dtype], M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
+                                          bias.data_ptr() if bias is not None else None, 1 if relu else 0,
+                                          out.data_ptr(), ldc)
     raise_for_status(rc)
 
 

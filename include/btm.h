@@ -117,6 +117,15 @@ int btm_check_device_status(int device, void *stream);
 int btm_gemm(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B,
              int64_t ldb, void *C, int64_t ldc);
 
+/* Fused epilogue: C[M,N] = act(A[M,K] . B[K,N] + bias[N]), where the bias (one value per output column, same
+ * dtype as C, or NULL for none) is added to the fp32 accumulator and the activation applied before the single
+ * rounding to the output type. This is the fusion of the product with the reference's element-wise Add
+ * (Ops/Elementwise/Add/Add.h:28, broadcast of a row vector) and Relu (Ops/Elementwise/Relu/Relu.h, an empty
+ * include guard) into the kernel that produces C, so C is written once. Everything else as btm_gemm. */
+enum btm_activation { BTM_ACT_NONE = 0, BTM_ACT_RELU = 1 };
+int btm_gemm_bias_act(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B,
+                      int64_t ldb, const void *bias, int act, void *C, int64_t ldc);
+
 /* C[M,N] = A[M,K] . Bt[N,K]^T: the same product with B supplied transposed (row-major [N,K], so both
  * operands are K-contiguous). This is the copy-free form of matmul(a, transpose(b)); the reference's
  * Ops/Algebra/Transpose is an empty stub (Ops/Algebra/Transpose/Transpose.h), so a BeanTensor
