@@ -277,6 +277,208 @@ int4_gemv_kernel(const __grid_constant__ CUtensorMap tmW, int M, int N, int K, i
     }
 }
 
+// Streaming GEMV for M <= 8: one persistent CTA per SM walks the 16-row weight blocks c, c + grid, ... and
+// keeps the weight stream running while it computes. A block's 16 rows are consecutive in memory (16 * K/2
+// bytes, and its scales one span of 16 * G halves); a producer warp brings them in with bulk copies (one per
+// row, so that the rows can be staged 64 bytes mod 128 apart: the lanes of one shared-memory access phase
+// read two neighbouring rows) into one of two stages (full / empty mbarriers). Eight computing warps each
+// own an eighth of K of every block and never meet on a CTA-wide barrier: a warp writes its partial sums,
+// counts itself in, and the warp that arrives last adds the partials in warp order (so the result does not
+// depend on arrival order) and stores the block's outputs.
+// The CTA uses less than half of an SM's shared memory and registers, and the grid is launched with
+// programmatic stream serialisation: the next int4 launch on the stream becomes resident beside this one
+// and streams its first blocks (weights and scales are parameters no predecessor writes) while this one is
+// still computing; its computing warps touch the activations only after griddepcontrol.wait. Back-to-back
+// launches (the layers of a decoder) therefore find their first blocks in shared memory when the predecessor
+// ends, which the one-slab-per-CTA kernel above cannot offer: its CTAs hold all of shared memory until they
+// exit.
+// Measured (N = 11008, K = 4096, M = 1, launches back to back): 8.9 us per launch against 10.0 us for the slab
+// kernel. Of that, 1.6 us pass between the predecessor's end and the return of griddepcontrol.wait, 0.5 us
+// stage the activations, and each of a CTA's four or five blocks takes 1.1 us of arithmetic although its data
+// is already in shared memory. That 1.1 us did not move with sixteen warps instead of eight, with half of the
+// mma instructions or all of the fp16 offset removal taken out, or with a CTA barrier instead of the counter;
+// packed-fp16 FMAs in place of the mma were slower (16.8 us).
+constexpr int GS_WARPS = 8;  // computing warps; warp GS_WARPS is the producer
+constexpr int GS_STAGES = 2; // weight blocks in flight per CTA
+constexpr int GS_RED = 3;    // partial-sum buffers: a warp is never more than two blocks ahead of another
+
+template <bool kStageAct>
+__global__ void __launch_bounds__((GS_WARPS + 1) * 32, 2)
+int4_gemv_stream_kernel(const uint8_t *__restrict__ w, int M, int N, int K, int group, const __half *__restrict__ act,
+                        const __half *__restrict__ scales, __half *__restrict__ out, int *status)
+{
+    // Shared memory: GS_STAGES x ([16 rows][K/2 B] weights + [16][G] fp16 scales) | GS_RED x [8 warps][16 rows][mrows]
+    // fp32 partials | [mrows][K/8 + 1] uint4 staged activations (kStageAct only).
+    extern __shared__ __align__(128) uint8_t wsm[];
+    __shared__ __align__(8) uint64_t bar_full[GS_STAGES], bar_empty[GS_STAGES];
+    __shared__ int arrived[GS_RED];
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int mrows = min(8, M);
+    const int nkb = K / 128;
+    const int kpw = (nkb + GS_WARPS - 1) / GS_WARPS; // 128-k blocks per warp
+    const int kb_lo = min(warp * kpw, nkb), kb_hi = min(kb_lo + kpw, nkb);
+    const int G = K / group;
+    const int row_bytes = K / 2;
+    // Rows are staged 64 bytes (mod 128) apart: the eight lanes of one shared-memory access phase read two
+    // neighbouring rows, which would otherwise fall on the same banks.
+    const int row_pitch = row_bytes + ((192 - (row_bytes & 127)) & 127);
+    const int w_bytes = GEMV_ROWS * row_pitch;
+    const int stage_bytes = w_bytes + GEMV_ROWS * G * 2; // multiple of 16: G is a multiple of 8 on this path
+    const int nblocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
+    const int my_blocks = ((int)blockIdx.x < nblocks) ? (nblocks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    float *red = reinterpret_cast<float *>(wsm + GS_STAGES * stage_bytes);
+    const int red_floats = GS_WARPS * 16 * mrows;
+    uint4 *act_s = reinterpret_cast<uint4 *>(wsm + GS_STAGES * stage_bytes + ((GS_RED * red_floats * 4 + 15) & ~15));
+    const int act_pitch = K / 8 + 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < GS_RED; ++i) arrived[i] = 0;
+        for (int i = 0; i < GS_STAGES; ++i) {
+            mbar_init(smem_u32(&bar_full[i]), 1);
+            mbar_init(smem_u32(&bar_empty[i]), GS_WARPS);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    // Programmatic dependent launch: this grid lets its successor start now. The producer never waits for the
+    // predecessor (it reads weights and scales only); the computing warps do, before they read the activations
+    // (which a predecessor may have produced) or write the output.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == GS_WARPS) {
+        // ------------------------------------------------------------ producer: two bulk copies per block
+        if (lane == 0) {
+            for (int bi = 0; bi < my_blocks; ++bi) {
+                const int stage = bi % GS_STAGES;
+                if (bi >= GS_STAGES &&
+                    !mbar_wait_short(smem_u32(&bar_empty[stage]), (uint32_t)((bi / GS_STAGES - 1) & 1), &abort_flag, status, WAIT_PRODUCER_EMPTY))
+                    break;
+                const int n0 = ((int)blockIdx.x + bi * (int)gridDim.x) * GEMV_ROWS;
+                const int rows = min(GEMV_ROWS, N - n0); // rows past N are not read
+                const uint32_t dst = smem_u32(wsm) + (uint32_t)stage * (uint32_t)stage_bytes;
+                mbar_expect_tx(smem_u32(&bar_full[stage]), (uint32_t)(rows * (row_bytes + G * 2)));
+                bulk_g2s(dst + (uint32_t)w_bytes, scales + (size_t)n0 * G, (uint32_t)(rows * G * 2), smem_u32(&bar_full[stage]));
+                for (int r = 0; r < rows; ++r) // the rows are consecutive in memory: HBM still sees one sequential read
+                    bulk_g2s(dst + (uint32_t)(r * row_pitch), w + (size_t)(n0 + r) * row_bytes, (uint32_t)row_bytes, smem_u32(&bar_full[stage]));
+            }
+        }
+    } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if constexpr (kStageAct) {
+            // 8 consecutive activations -> {k0,k4}, {k1,k5}, {k2,k6}, {k3,k7}: the slot order of the unpacked weights
+            const int act_total = mrows * (K / 8);
+            for (int i = threadIdx.x; i < act_total; i += GS_WARPS * 32) {
+                const uint4 r = __ldg(reinterpret_cast<const uint4 *>(act) + i);
+                uint4 o;
+                o.x = __byte_perm(r.x, r.z, 0x5410);
+                o.y = __byte_perm(r.x, r.z, 0x7632);
+                o.z = __byte_perm(r.y, r.w, 0x5410);
+                o.w = __byte_perm(r.y, r.w, 0x7632);
+                act_s[i + (i >= K / 8 ? 1 : 0)] = o; // at most two staged rows
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory"); // the computing warps' own barrier (GS_WARPS * 32 threads), once
+        }
+        // Lane (g, t) supplies activation row g to the mma's B operand; columns past the last row are never stored,
+        // so their lanes load nothing (a shared-memory access with four active lanes is one wavefront, not four).
+        const bool has_row = g < mrows;
+        const uint4 *arow = reinterpret_cast<const uint4 *>(act + (size_t)min(g, mrows - 1) * K) + t * 4;
+        const uint4 *arow_s = act_s + min(g, mrows - 1) * act_pitch + t * 4;
+        const int bpg = group / 128;
+
+#pragma unroll 1
+        for (int bi = 0; bi < my_blocks; ++bi) {
+            const int stage = bi % GS_STAGES, slot = bi % GS_RED;
+            const int n0 = ((int)blockIdx.x + bi * (int)gridDim.x) * GEMV_ROWS;
+            float tot[4] = {0.f, 0.f, 0.f, 0.f};
+            if (!mbar_wait_warp(smem_u32(&bar_full[stage]), (uint32_t)((bi / GS_STAGES) & 1), &abort_flag, status, WAIT_EPI_STAGE)) break;
+            const uint8_t *st_base = wsm + (size_t)stage * stage_bytes;
+            const uint8_t *rowA = st_base + (size_t)g * row_pitch + t * 16;
+            const uint8_t *rowB = rowA + 8 * (size_t)row_pitch;
+            const __half *sA = reinterpret_cast<const __half *>(st_base + w_bytes) + g * G;
+            const __half *sB = sA + 8 * G;
+#pragma unroll 1
+            for (int kb = kb_lo; kb < kb_hi; ++kb) {
+                const uint4 qa = *reinterpret_cast<const uint4 *>(rowA + kb * 64);
+                const uint4 qb = *reinterpret_cast<const uint4 *>(rowB + kb * 64);
+                const uint32_t xa[4] = {qa.x, qa.y, qa.z, qa.w};
+                const uint32_t xb[4] = {qb.x, qb.y, qb.z, qb.w};
+                const int si = bpg == 1 ? kb : (int)((unsigned)kb / (unsigned)bpg);
+                const float sa = __half2float(sA[si]);
+                const float sb = __half2float(sB[si]);
+                {
+                    float c0[4], c1[4];
+#pragma unroll
+                    for (int wd = 0; wd < 4; ++wd) {
+                        uint4 av = make_uint4(0u, 0u, 0u, 0u);
+                        if (has_row) av = kStageAct ? arow_s[kb * 16 + wd] : __ldg(arow + kb * 16 + wd);
+                        uint32_t ha[4], hb[4];
+                        unpack8(xa[wd], ha);
+                        unpack8(xb[wd], hb);
+                        const uint32_t b04 = kStageAct ? av.x : __byte_perm(av.x, av.z, 0x5410);
+                        const uint32_t b15 = kStageAct ? av.y : __byte_perm(av.x, av.z, 0x7632);
+                        const uint32_t b26 = kStageAct ? av.z : __byte_perm(av.y, av.w, 0x5410);
+                        const uint32_t b37 = kStageAct ? av.w : __byte_perm(av.y, av.w, 0x7632);
+                        if (wd == 0) {
+                            mma_16816_first(c0, ha[0], hb[0], ha[1], hb[1], b04, b15);
+                            mma_16816_first(c1, ha[2], hb[2], ha[3], hb[3], b26, b37);
+                        } else {
+                            mma_16816(c0, ha[0], hb[0], ha[1], hb[1], b04, b15);
+                            mma_16816(c1, ha[2], hb[2], ha[3], hb[3], b26, b37);
+                        }
+                    }
+                    tot[0] = fmaf(sa, c0[0] + c1[0], tot[0]);
+                    tot[1] = fmaf(sa, c0[1] + c1[1], tot[1]);
+                    tot[2] = fmaf(sb, c0[2] + c1[2], tot[2]);
+                    tot[3] = fmaf(sb, c0[3] + c1[3], tot[3]);
+                }
+            }
+            // This warp's words and scales of the stage are consumed: hand the stage back.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_empty[stage]));
+            float *mine = red + slot * red_floats + warp * 16 * mrows;
+            {
+                // Partials [warp][row][m] of the valid activation rows; accumulator columns are m = 2t, 2t + 1.
+                if (2 * t < mrows) {
+                    mine[g * mrows + 2 * t] = tot[0];
+                    mine[(g + 8) * mrows + 2 * t] = tot[2];
+                }
+                if (2 * t + 1 < mrows) {
+                    mine[g * mrows + 2 * t + 1] = tot[1];
+                    mine[(g + 8) * mrows + 2 * t + 1] = tot[3];
+                }
+            }
+            __threadfence_block();
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) last = atomicAdd(&arrived[slot], 1) == GS_WARPS - 1;
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence_block();
+                // The last warp to arrive adds the partials in warp order and stores the block.
+                for (int o = lane; o < 16 * mrows; o += 32) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int wi = 0; wi < GS_WARPS; ++wi) sum += red[slot * red_floats + wi * 16 * mrows + o];
+                    const int r = o / mrows, m = o - r * mrows;
+                    if (n0 + r < N) out[(size_t)m * N + n0 + r] = __float2half_rn(sum);
+                }
+                __syncwarp();
+                if (lane == 0) arrived[slot] = 0; // reused three blocks on, after every warp has passed this block
+            }
+        }
+    }
+    __syncthreads();
+    if (abort_flag) {
+        // A wait ran out: give copies still in flight a bounded time to land before the CTA's shared
+        // memory is released.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+    }
+}
+
 // Eight nibbles of one word -> four half2 in NATURAL pair order {k0,k1}, {k2,k3}, {k4,k5}, {k6,k7}, so that
 // activations can be used as they lie in memory. A byte-permute puts each byte in both halves of a word;
 // (x & 0x00F0000F) ^ 0x64806408 then makes {1032 + v_even, 1152 + 16 v_odd} and one HFMA2 with per-half
@@ -535,7 +737,6 @@ static int grid_for(long long items, int block, int sm_cap)
 int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
                      const void *scales, void *out, int *status)
 {
-    (void)sm_count;
     if (M == 0 || N == 0) return BTM_OK;
     const bool fast = (K % 128 == 0) && (group % 128 == 0) && (((uintptr_t)act & 15) == 0) && (((uintptr_t)w & 15) == 0) &&
                       (((uintptr_t)scales & 1) == 0) && K > 0 && (size_t)GEMV_ROWS * (K / 2 + GEMV_ROW_PAD + 2 * (K / group)) + 2 * (size_t)(K / 8 + 1) * 16 <= 200 * 1024;
@@ -572,9 +773,46 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
         if (rc) return rc;
         return check_cuda(cudaGetLastError(), "int4 gemm launch");
     }
-    dim3 grid((unsigned)((N + GEMV_ROWS - 1) / GEMV_ROWS), (unsigned)((M + 7) / 8));
     const bool stage_act = M <= 2;
     const int npieces = (K / 128 + 1) / 2;
+    // Streaming kernel: K long enough to give each of its eight warps a 128-k block, a block's scales a whole
+    // number of 16-byte units at a 16-byte-aligned address, and two stages plus the partial sums and the staged
+    // activations within half an SM's shared memory.
+    const char *force_gemv = getenv("BTM_FORCE_GEMV");
+    const int mrows_s = M < 8 ? M : 8;
+    const size_t smem_stream = (size_t)GS_STAGES * GEMV_ROWS * (K / 2 + ((192 - ((K / 2) & 127)) & 127) + (K / group) * 2) + (((size_t)GS_RED * GS_WARPS * 16 * mrows_s * 4 + 15) & ~(size_t)15) +
+                               (stage_act ? (size_t)M * (K / 8 + 1) * sizeof(uint4) : 0);
+    const bool stream_ok = K / 128 >= GS_WARPS && (K / 2) % 16 == 0 && (K / group) % 8 == 0 && (((uintptr_t)scales & 15) == 0) &&
+                           smem_stream <= 100 * 1024 && !(force_gemv && !strcmp(force_gemv, "slab"));
+    if (stream_ok) {
+        const void *fn = stage_act ? (const void *)int4_gemv_stream_kernel<true> : (const void *)int4_gemv_stream_kernel<false>;
+        static bool configured[2] = {false, false}; // the attribute is per function and idempotent
+        const int fi = stage_act ? 1 : 0;
+        if (!configured[fi]) {
+            int rcs = check_cuda(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024), "cudaFuncSetAttribute(int4_gemv_stream)");
+            if (rcs) return rcs;
+            configured[fi] = true;
+        }
+        const int nblocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(nblocks < sm_count ? nblocks : sm_count));
+        cfg.blockDim = dim3((GS_WARPS + 1) * 32);
+        cfg.dynamicSmemBytes = smem_stream;
+        cfg.stream = st;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization; // the kernel orders itself with griddepcontrol
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        const __half *act_h = (const __half *)act, *sc_h = (const __half *)scales;
+        const uint8_t *w_b = (const uint8_t *)w;
+        __half *out_h = (__half *)out;
+        void *args[] = {(void *)&w_b, (void *)&M, (void *)&N, (void *)&K, (void *)&group, (void *)&act_h, (void *)&sc_h, (void *)&out_h, (void *)&status};
+        cudaError_t le = cudaLaunchKernelExC(&cfg, fn, args);
+        if (le != cudaSuccess) return check_cuda(le, "int4 gemv launch");
+        return check_cuda(cudaGetLastError(), "int4 gemv launch");
+    }
+    dim3 grid((unsigned)((N + GEMV_ROWS - 1) / GEMV_ROWS), (unsigned)((M + 7) / 8));
     if (npieces > GEMV_MAX_PIECES) return set_error(BTM_ERR_UNSUPPORTED, "int4 matmul: K=%d is beyond the fast kernel's limit of %d", K, GEMV_MAX_PIECES * 256);
     CUtensorMap tmW;
     int rc = encode_tmap_3d(&tmW, BTM_U8, w, (uint64_t)K / 2, (uint64_t)N, 1, (uint64_t)K / 2, (uint64_t)K / 2, 128, GEMV_ROWS, false);
