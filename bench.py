@@ -41,6 +41,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 NCU_TRAFFIC = {
     "gemm_f16_4096": 105.9e6,  # profiles/gemm_tc2_f16_4096.md (89.0 MB read + 16.9 MB written)
     "int4_gemv_m1": 23.3e6,  # profiles/int4_gemv_m1.md (read; nothing written back within the kernel)
+    # profiles/bmm_64x512x512x128.md: 16.8 MB read (A and B), 0.03 MB written: the 33.6 MB of C were still in the
+    # 126 MB L2 when the kernel ended, so they do not show in the kernel's own DRAM counters
+    "bmm": 16.9e6,
 }
 
 
@@ -368,7 +371,7 @@ def bench_bmm(torch, ops, peaks, steps, warmup):
             "launch": f"CUDA graph of {sets} launches, replayed", "algorithmic_bytes": algo,
             "value": gbs, "unit": "GB/s", "tflops": tf,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": gbs / peaks["hbm_gbs"], "frac_nominal": gbs / NOMINAL_HBM_GBS, "traffic": None},
+                         "frac": gbs / peaks["hbm_gbs"], "frac_nominal": gbs / NOMINAL_HBM_GBS, "traffic": NCU_TRAFFIC["bmm"]},
             "l2": f"{sets} rotating buffer sets ({sets * algo >> 20} MiB > L2)"}
 
 
