@@ -82,6 +82,7 @@ DeviceState *device_state(int device)
     if (configure_gemm_tc_kernels()) return nullptr;
     if (configure_gemm_tc2_kernels()) return nullptr;
     if (configure_int4_tc_kernels()) return nullptr;
+    if (configure_int4_gemv_kernels()) return nullptr;
     ds->sm_count = prop.multiProcessorCount;
     ds->ws = nullptr;
     ds->ws_bytes = 0;

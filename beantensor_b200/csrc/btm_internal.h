@@ -77,6 +77,7 @@ int launch_int4_quantize(cudaStream_t st, int N, int K, int group, const void *w
 int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once per device
 int configure_gemm_tc2_kernels();
 int configure_int4_tc_kernels();
+int configure_int4_gemv_kernels();
 int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const void *act, const void *w, const void *scales, void *out,
                         int *status, int sm_count);
 int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,

@@ -734,6 +734,13 @@ static int grid_for(long long items, int block, int sm_cap)
     return (int)g;
 }
 
+int configure_int4_gemv_kernels()
+{
+    cudaError_t e = cudaFuncSetAttribute(int4_gemv_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(int4_gemv_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    return check_cuda(e, "cudaFuncSetAttribute(int4_gemv_stream)");
+}
+
 int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
                      const void *scales, void *out, int *status)
 {
@@ -786,13 +793,6 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
                            smem_stream <= 100 * 1024 && !(force_gemv && !strcmp(force_gemv, "slab"));
     if (stream_ok) {
         const void *fn = stage_act ? (const void *)int4_gemv_stream_kernel<true> : (const void *)int4_gemv_stream_kernel<false>;
-        static bool configured[2] = {false, false}; // the attribute is per function and idempotent
-        const int fi = stage_act ? 1 : 0;
-        if (!configured[fi]) {
-            int rcs = check_cuda(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024), "cudaFuncSetAttribute(int4_gemv_stream)");
-            if (rcs) return rcs;
-            configured[fi] = true;
-        }
         const int nblocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(nblocks < sm_count ? nblocks : sm_count));

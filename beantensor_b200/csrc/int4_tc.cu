@@ -14,11 +14,13 @@
 //   warp 0      TMA: packed weights, 128 rows x 64 B (64-byte swizzle), ring of 3-4 units;
 //   warp 2      TMA: activation tiles, MB rows x 64 k (K-major, 128-byte swizzle), two per unit;
 //   warps 3-10  dequantise: thread = (weight row, 64-k block of the unit); two 128-bit shared loads,
-//               unpack to exact fp16 integers in natural k order, multiply by the group scale, write
-//               the row of the 128 x 64 fp16 tile in the K-major 128-byte-swizzled layout the tensor
-//               core reads. The dequantisation is the critical resource (about two instructions per
-//               weight), hence eight warps per CTA and two CTAs per SM;
-//   warp 1      tcgen05.mma (M = 128, N = MB, both operands K-major); tcgen05.commit frees the stages.
+//               unpack to exact fp16 integers in natural k order, multiply by the group scale, and
+//               write the row's 64 fp16 straight into tensor memory (tcgen05.st, 32 columns of the
+//               thread's own lane): the tensor core takes its A operand from there, so the tile never
+//               passes through shared memory and needs no proxy fence. Eight warps per CTA and two
+//               CTAs per SM: the dequantisation is the critical resource;
+//   warp 1      tcgen05.mma (M = 128, N = MB, A from tensor memory, B K-major in shared memory);
+//               tcgen05.commit frees the stages.
 // Then every CTA reads its accumulator (lane = weight row, column = activation row); CTAs 1.. of the
 // cluster store theirs into CTA 0's shared memory (column-major, so a warp writes 128 contiguous bytes),
 // and CTA 0 adds the partials in rank order, rounds once to fp16, transposes the tile through shared
@@ -64,8 +66,8 @@ constexpr int BW = 128;            // weight rows per CTA = UMMA M
 constexpr int BKE = 64;            // k per operand stage
 constexpr int UNIT_K = 128;        // k per raw-weight unit (64 bytes per row)
 constexpr int RAW_BYTES = BW * 64; // 8 KB
-constexpr int W_BYTES = BW * 128;  // dequantised tile: 128 rows x 64 k fp16
-constexpr int W_STAGES = 3;
+constexpr int W_COLS = 32;         // dequantised tile in tensor memory: 128 lanes x 32 columns = 128 rows x 64 k fp16
+constexpr int TMEM_COLS = 256;     // accumulator (MB columns) + ring of dequantised tiles
 constexpr int THREADS = 352;       // warp 0 weight TMA, 1 MMA, 2 activation TMA, 3..10 dequantise + epilogue
 constexpr int DQ_FIRST = 96;       // first dequantising thread
 constexpr int MAX_SPLIT = 3;
@@ -75,10 +77,11 @@ constexpr int RED_BYTES = RED_FLOATS * 4; // one CTA's partials for one round (3
 constexpr int OUT_TILE_OFF = (MAX_SPLIT - 1) * RED_BYTES; // fp16 [64 m][128 n] staging behind the partials
 template <int MB> // activation rows per pass: 64 or 128 (= UMMA N = accumulator columns)
 struct Cfg {
-    static constexpr int RAW_STAGES = MB == 64 ? 4 : 3;
-    static constexpr int ACT_STAGES = MB == 64 ? 3 : 2;
+    static constexpr int RAW_STAGES = MB == 64 ? 6 : 4;
+    static constexpr int ACT_STAGES = MB == 64 ? 6 : 4;
+    static constexpr int W_STAGES = (TMEM_COLS - MB) / W_COLS; // 6 or 4 tiles in tensor memory
     static constexpr int ACT_BYTES = MB * 128;
-    static constexpr int RING_BYTES = W_STAGES * W_BYTES + ACT_STAGES * ACT_BYTES + RAW_STAGES * RAW_BYTES;
+    static constexpr int RING_BYTES = ACT_STAGES * ACT_BYTES + RAW_STAGES * RAW_BYTES;
     // After the main loop the rings are dead and hold the other CTAs' partial accumulators and the output tile.
     static_assert(OUT_TILE_OFF + RED_COLS * BW * 2 <= RING_BYTES, "reduction buffers must fit in the rings");
     static constexpr int SMEM_BYTES = RING_BYTES + 1024; // + BW * groups-in-slice * 2 bytes of scales at run time
@@ -128,7 +131,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
 {
     using namespace i4tc;
     using C = Cfg<MB>;
-    constexpr int RAW_STAGES = C::RAW_STAGES, ACT_STAGES = C::ACT_STAGES;
+    constexpr int RAW_STAGES = C::RAW_STAGES, ACT_STAGES = C::ACT_STAGES, W_STAGES = C::W_STAGES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_raw_full[RAW_STAGES], bar_raw_empty[RAW_STAGES];
     __shared__ __align__(8) uint64_t bar_act_full[ACT_STAGES], bar_act_empty[ACT_STAGES], bar_w_full[W_STAGES], bar_w_empty[W_STAGES];
@@ -139,8 +142,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t w_ring = smem_base;
-    const uint32_t act_ring = w_ring + W_STAGES * W_BYTES;
+    const uint32_t act_ring = smem_base;
     const uint32_t raw_ring = act_ring + ACT_STAGES * C::ACT_BYTES;
     __half *sc_s = reinterpret_cast<__half *>(smem_al + C::RING_BYTES);
 
@@ -186,7 +188,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         }
     }
     if (warp == 1) {
-        tmem_alloc<1>(smem_u32(&tmem_base_holder), MB);
+        tmem_alloc<1>(smem_u32(&tmem_base_holder), TMEM_COLS);
         tmem_relinquish<1>();
     }
     if (warp == 2 && lane == 0) prefetch_tmap(&tmAct);
@@ -240,12 +242,11 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
                     break;
                 }
                 tc_fence_after();
-                const uint32_t w0 = w_ring + ws * W_BYTES, a0 = act_ring + as * C::ACT_BYTES;
+                const uint32_t w0 = tmem_base + (uint32_t)(MB + ws * W_COLS), a0 = act_ring + as * C::ACT_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    const uint64_t wd = make_smem_desc_sw128(w0 + ks * 32, 16, 1024);
                     const uint64_t ad = make_smem_desc_sw128(a0 + ks * 32, 16, 1024);
-                    umma<1, false>(tmem_base, wd, ad, idesc, (i | ks) ? 1u : 0u);
+                    umma_a_tmem(tmem_base, w0 + (uint32_t)(ks * 8), ad, idesc, (i | ks) ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&bar_w_empty[ws])); // both tiles are free once these MMAs have read them
                 umma_commit(smem_u32(&bar_act_empty[as]));
@@ -258,8 +259,9 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         // ------------------------------------------------------------ dequantise (warps 3..10)
         // Thread = (weight row, which 64-k block of the unit): warps 3..6 fill the unit's first operand stage,
         // warps 7..10 the second, at the same time.
+        // A thread's row is the tensor-memory lane its warp may write: quadrant warp % 4.
         const int dq = threadIdx.x - DQ_FIRST; // 0..255
-        const int q = dq >> 7, row = dq & 127;
+        const int q = (warp - 3) >> 2, row = (warp & 3) * 32 + lane;
         // The eight warps fetch the slice's scales together, right away (a load issued once the weight
         // stream is queued would come back last), and meet on a named barrier of their own.
         const int G = p.K / group;
@@ -269,10 +271,10 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const __half *srow = sc_s + row * g_cnt - g_first;
-        const uint32_t xs = (uint32_t)((row >> 1) & 3), swz = (uint32_t)(row & 7);
+        const uint32_t xs = (uint32_t)((row >> 1) & 3);
         const uint32_t raw_row0 = raw_ring + (uint32_t)row * 64u;
         const uint32_t c0 = ((uint32_t)(2 * q) ^ xs) << 4, c1 = ((uint32_t)(2 * q + 1) ^ xs) << 4;
-        int rs = 0, ws = q; // block ordinal b = 2 i + q uses operand stage b % 3
+        int rs = 0, ws = q; // block ordinal b = 2 i + q uses operand stage b % W_STAGES (W_STAGES is even)
         uint32_t rphase = 0, wphase = 0;
         bool ok = n_units > 0 && mbar_wait_short_warp(smem_u32(&bar_raw_full[0]), 0u, &abort_flag, p.status, WAIT_EPI_STAGE);
         uint4 pa, pb; // 32 packed bytes = 64 nibbles of this row: k = u*128 + q*64 .. +64
@@ -304,13 +306,14 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             }
             ok = mbar_wait_short_warp(smem_u32(&bar_w_empty[ws]), wphase ^ 1u, &abort_flag, p.status, WAIT_EPI_STAGE);
             if (!ok) break;
-            const uint32_t wrow = w_ring + ws * W_BYTES + (uint32_t)row * 128u;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) st_shared_v4(wrow + ((((uint32_t)j) ^ swz) << 4), d[j].x, d[j].y, d[j].z, d[j].w);
-            fence_proxy_async_smem(); // generic-proxy writes -> visible to the tensor core's reads
+            tc_fence_after(); // the MMAs that read this tile have completed (their commit released it)
+            // 64 fp16 of this row = 32 columns of its tensor-memory lane, two consecutive k per column
+            tmem_st_32x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(MB + ws * W_COLS), *reinterpret_cast<const uint32_t(*)[32]>(&d[0]));
+            tmem_st_wait();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_w_full[ws]));
-            ws += 2; // two blocks further on: stage (b + 2) % 3, parity flips when the ordinal passes a multiple of 3
+            ws += 2; // two blocks further on
             if (ws >= W_STAGES) { ws -= W_STAGES; wphase ^= 1u; }
         }
         if (ok) mbar_wait_warp(smem_u32(&bar_acc_full), 0u, &abort_flag, p.status, WAIT_EPI_TMEM_FULL);
@@ -392,7 +395,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc<1>(tmem_base, MB);
+        tmem_dealloc<1>(tmem_base, TMEM_COLS);
     }
 }
 
