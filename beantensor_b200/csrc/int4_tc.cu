@@ -13,10 +13,10 @@
 // Roles in a CTA (7 warps), per 128-k unit of its K slice:
 //   warp 0      TMA: packed weights, 128 rows x 64 B (64-byte swizzle), ring of 3-4 units;
 //   warp 2      TMA: activation tiles, MB rows x 64 k (K-major, 128-byte swizzle), two per unit;
-//   warps 3-10  dequantise: thread = (weight row, 64-k block of the unit); two 128-bit shared loads,
-//               unpack to exact fp16 integers in natural k order, multiply by the group scale, and
-//               write the row's 64 fp16 straight into tensor memory (tcgen05.st, 32 columns of the
-//               thread's own lane): the tensor core takes its A operand from there, so the tile never
+//   warps 3-10  dequantise: thread = weight row, the two groups of four warps take alternate units; four
+//               128-bit shared loads, unpack to exact fp16 integers in natural k order, multiply by
+//               the group scale, and write the row's 128 fp16 straight into tensor memory (tcgen05.st,
+//               64 columns of the thread's own lane): the tensor core takes its A operand from there, so the tile never
 //               passes through shared memory and needs no proxy fence. Eight warps per CTA and two
 //               CTAs per SM: the dequantisation is the critical resource;
 //   warp 1      tcgen05.mma (M = 128, N = MB, A from tensor memory, B K-major in shared memory);
@@ -66,7 +66,7 @@ constexpr int BW = 128;            // weight rows per CTA = UMMA M
 constexpr int BKE = 64;            // k per operand stage
 constexpr int UNIT_K = 128;        // k per raw-weight unit (64 bytes per row)
 constexpr int RAW_BYTES = BW * 64; // 8 KB
-constexpr int W_COLS = 32;         // dequantised tile in tensor memory: 128 lanes x 32 columns = 128 rows x 64 k fp16
+constexpr int W_COLS = 64;         // dequantised unit in tensor memory: 128 lanes x 64 columns = 128 rows x 128 k fp16
 constexpr int TMEM_COLS = 256;     // accumulator (MB columns) + ring of dequantised tiles
 constexpr int THREADS = 352;       // warp 0 weight TMA, 1 MMA, 2 activation TMA, 3..10 dequantise + epilogue
 constexpr int DQ_FIRST = 96;       // first dequantising thread
@@ -79,7 +79,7 @@ template <int MB> // activation rows per pass: 64 or 128 (= UMMA N = accumulator
 struct Cfg {
     static constexpr int RAW_STAGES = MB == 64 ? 6 : 4;
     static constexpr int ACT_STAGES = MB == 64 ? 6 : 4;
-    static constexpr int W_STAGES = (TMEM_COLS - MB) / W_COLS; // 6 or 4 tiles in tensor memory
+    static constexpr int W_STAGES = (TMEM_COLS - MB) / W_COLS; // 3 or 2 units in tensor memory
     static constexpr int ACT_BYTES = MB * 128;
     static constexpr int RING_BYTES = ACT_STAGES * ACT_BYTES + RAW_STAGES * RAW_BYTES;
     // After the main loop the rings are dead and hold the other CTAs' partial accumulators and the output tile.
@@ -168,7 +168,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         abort_flag = 0;
         for (int i = 0; i < RAW_STAGES; ++i) {
             mbar_init(smem_u32(&bar_raw_full[i]), 1);
-            mbar_init(smem_u32(&bar_raw_empty[i]), 8);
+            mbar_init(smem_u32(&bar_raw_empty[i]), 4);
         }
         for (int i = 0; i < ACT_STAGES; ++i) {
             mbar_init(smem_u32(&bar_act_full[i]), 1);
@@ -235,33 +235,36 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             int as = 0, ws = 0;
             uint32_t aphase = 0, wphase = 0;
             bool ok = true;
-            for (int i = 0; ok && i < n_units * (UNIT_K / BKE); ++i) {
-                if (!mbar_wait_short(smem_u32(&bar_act_full[as]), aphase, &abort_flag, p.status, WAIT_MMA_FULL) ||
-                    !mbar_wait_short(smem_u32(&bar_w_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t w0 = tmem_base + (uint32_t)(MB + ws * W_COLS), a0 = act_ring + as * C::ACT_BYTES;
+            for (int i = 0; ok && i < n_units; ++i) {
+                if (!mbar_wait_short(smem_u32(&bar_w_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL)) break;
+                for (int q = 0; q < UNIT_K / BKE; ++q) {
+                    if (!mbar_wait_short(smem_u32(&bar_act_full[as]), aphase, &abort_flag, p.status, WAIT_MMA_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t w0 = tmem_base + (uint32_t)(MB + ws * W_COLS + q * 32), a0 = act_ring + as * C::ACT_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    const uint64_t ad = make_smem_desc_sw128(a0 + ks * 32, 16, 1024);
-                    umma_a_tmem(tmem_base, w0 + (uint32_t)(ks * 8), ad, idesc, (i | ks) ? 1u : 0u);
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t ad = make_smem_desc_sw128(a0 + ks * 32, 16, 1024);
+                        umma_a_tmem(tmem_base, w0 + (uint32_t)(ks * 8), ad, idesc, (i | q | ks) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&bar_act_empty[as])); // the activation tile is free once these MMAs have read it
+                    if (++as == ACT_STAGES) { as = 0; aphase ^= 1u; }
                 }
-                umma_commit(smem_u32(&bar_w_empty[ws])); // both tiles are free once these MMAs have read them
-                umma_commit(smem_u32(&bar_act_empty[as]));
-                if (++as == ACT_STAGES) { as = 0; aphase ^= 1u; }
+                umma_commit(smem_u32(&bar_w_empty[ws])); // ... and the unit in tensor memory after both of its blocks
                 if (++ws == W_STAGES) { ws = 0; wphase ^= 1u; }
             }
             if (ok) umma_commit(smem_u32(&bar_acc_full));
         }
     } else {
         // ------------------------------------------------------------ dequantise (warps 3..10)
-        // Thread = (weight row, which 64-k block of the unit): warps 3..6 fill the unit's first operand stage,
-        // warps 7..10 the second, at the same time.
+        // Thread = weight row; warps 3..6 take the even units of the CTA's walk, warps 7..10 the odd ones, each
+        // unit whole (128 k = 64 columns of the row's tensor-memory lane), so that a warp passes one set of
+        // hand-offs (weight ring, operand stage, store fence) per 128 k instead of per 64.
         // A thread's row is the tensor-memory lane its warp may write: quadrant warp % 4.
         const int dq = threadIdx.x - DQ_FIRST; // 0..255
-        const int q = (warp - 3) >> 2, row = (warp & 3) * 32 + lane;
+        const int grp = (warp - 3) >> 2, row = (warp & 3) * 32 + lane;
         // The eight warps fetch the slice's scales together, right away (a load issued once the weight
         // stream is queued would come back last), and meet on a named barrier of their own.
         const int G = p.K / group;
@@ -273,48 +276,49 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         const __half *srow = sc_s + row * g_cnt - g_first;
         const uint32_t xs = (uint32_t)((row >> 1) & 3);
         const uint32_t raw_row0 = raw_ring + (uint32_t)row * 64u;
-        const uint32_t c0 = ((uint32_t)(2 * q) ^ xs) << 4, c1 = ((uint32_t)(2 * q + 1) ^ xs) << 4;
-        int rs = 0, ws = q; // block ordinal b = 2 i + q uses operand stage b % W_STAGES (W_STAGES is even)
-        uint32_t rphase = 0, wphase = 0;
-        bool ok = n_units > 0 && mbar_wait_short_warp(smem_u32(&bar_raw_full[0]), 0u, &abort_flag, p.status, WAIT_EPI_STAGE);
-        uint4 pa, pb; // 32 packed bytes = 64 nibbles of this row: k = u*128 + q*64 .. +64
-        if (ok) {
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(pa.x), "=r"(pa.y), "=r"(pa.z), "=r"(pa.w) : "r"(raw_row0 + c0));
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(pb.x), "=r"(pb.y), "=r"(pb.z), "=r"(pb.w) : "r"(raw_row0 + c1));
-        }
-        for (int i = 0; ok && i < n_units; ++i) {
+        const uint32_t tmem_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)MB;
+        bool ok = true;
+        for (int i = grp; ok && i < n_units; i += 2) {
             const int u = unit_at(i);
-            const __half2 s2 = __half2half2(srow[((u * 2 + q) * BKE) / group]);
-            uint4 d[8];
-            d[0] = dequant_word(pa.x, s2);
-            d[1] = dequant_word(pa.y, s2);
-            d[2] = dequant_word(pa.z, s2);
-            d[3] = dequant_word(pa.w, s2);
-            d[4] = dequant_word(pb.x, s2);
-            d[5] = dequant_word(pb.y, s2);
-            d[6] = dequant_word(pb.z, s2);
-            d[7] = dequant_word(pb.w, s2);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_raw_empty[rs])); // this warp's part of the unit is in registers
-            if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1u; }
-            if (i + 1 < n_units) { // the next unit's packed words are fetched before this one's stores
-                ok = mbar_wait_short_warp(smem_u32(&bar_raw_full[rs]), rphase, &abort_flag, p.status, WAIT_EPI_STAGE);
-                if (!ok) break;
-                const uint32_t rr = raw_row0 + rs * RAW_BYTES;
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(pa.x), "=r"(pa.y), "=r"(pa.z), "=r"(pa.w) : "r"(rr + c0));
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(pb.x), "=r"(pb.y), "=r"(pb.z), "=r"(pb.w) : "r"(rr + c1));
-            }
-            ok = mbar_wait_short_warp(smem_u32(&bar_w_empty[ws]), wphase ^ 1u, &abort_flag, p.status, WAIT_EPI_STAGE);
+            const int rs = i % RAW_STAGES, ws = i % W_STAGES;
+            ok = mbar_wait_short_warp(smem_u32(&bar_raw_full[rs]), (uint32_t)((i / RAW_STAGES) & 1), &abort_flag, p.status, WAIT_EPI_STAGE);
             if (!ok) break;
-            tc_fence_after(); // the MMAs that read this tile have completed (their commit released it)
+            uint4 pw[4]; // 64 packed bytes = 128 nibbles of this row, k = u*128 .. +128
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(pw[c].x), "=r"(pw[c].y), "=r"(pw[c].z), "=r"(pw[c].w)
+                             : "r"(raw_row0 + rs * RAW_BYTES + ((((uint32_t)c) ^ xs) << 4)));
+            const __half2 s0 = __half2half2(srow[(u * UNIT_K) / group]), s1 = __half2half2(srow[(u * UNIT_K + BKE) / group]);
+            uint4 d[8];
+            d[0] = dequant_word(pw[0].x, s0);
+            d[1] = dequant_word(pw[0].y, s0);
+            d[2] = dequant_word(pw[0].z, s0);
+            d[3] = dequant_word(pw[0].w, s0);
+            d[4] = dequant_word(pw[1].x, s0);
+            d[5] = dequant_word(pw[1].y, s0);
+            d[6] = dequant_word(pw[1].z, s0);
+            d[7] = dequant_word(pw[1].w, s0);
+            ok = mbar_wait_short_warp(smem_u32(&bar_w_empty[ws]), (uint32_t)((i / W_STAGES) & 1) ^ 1u, &abort_flag, p.status, WAIT_EPI_STAGE);
+            if (!ok) break;
+            tc_fence_after(); // the MMAs that read this stage have completed (their commit released it)
             // 64 fp16 of this row = 32 columns of its tensor-memory lane, two consecutive k per column
-            tmem_st_32x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(MB + ws * W_COLS), *reinterpret_cast<const uint32_t(*)[32]>(&d[0]));
+            tmem_st_32x32(tmem_row + (uint32_t)(ws * W_COLS), *reinterpret_cast<const uint32_t(*)[32]>(&d[0]));
+            d[0] = dequant_word(pw[2].x, s1);
+            d[1] = dequant_word(pw[2].y, s1);
+            d[2] = dequant_word(pw[2].z, s1);
+            d[3] = dequant_word(pw[2].w, s1);
+            d[4] = dequant_word(pw[3].x, s1);
+            d[5] = dequant_word(pw[3].y, s1);
+            d[6] = dequant_word(pw[3].z, s1);
+            d[7] = dequant_word(pw[3].w, s1);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_raw_empty[rs])); // this warp's rows of the unit are in registers
+            tmem_st_32x32(tmem_row + (uint32_t)(ws * W_COLS + 32), *reinterpret_cast<const uint32_t(*)[32]>(&d[0]));
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_w_full[ws]));
-            ws += 2; // two blocks further on
-            if (ws >= W_STAGES) { ws -= W_STAGES; wphase ^= 1u; }
         }
         if (ok) mbar_wait_warp(smem_u32(&bar_acc_full), 0u, &abort_flag, p.status, WAIT_EPI_TMEM_FULL);
         tc_fence_after();
