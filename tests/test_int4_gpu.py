@@ -134,3 +134,29 @@ def test_more_than_eight_rows_both_paths(btm, oracle, case, path, monkeypatch):
         dq = oracle.int4_dequant(packed, s.view(np.uint16), group)
         ref_dq = oracle.gemm(oracle.F16, act.view(np.uint16), np.ascontiguousarray(dq.T))
         assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, ref_dq) <= 5e-4
+
+
+def _seeded_shapes():
+    # A fixed pseudo-random walk over shapes that reach every int4 kernel: GEMV (streaming and slab), the
+    # tcgen05 kernel with 1..3-way K splits, one and two 128-row passes, partial tiles, several group sizes.
+    rng = np.random.default_rng(20240607)
+    cases = []
+    for _ in range(28):
+        M = int(rng.choice([1, 2, 3, 5, 8, 9, 16, 31, 64, 65, 100, 128, 130, 200]))
+        K = int(rng.choice([128, 256, 512, 1024, 1536, 2048, 4096]))
+        divisors = [g for g in (64, 128, 256, 512, 1024) if K % g == 0]
+        group = int(rng.choice(divisors))
+        N = int(rng.choice([1, 7, 16, 33, 100, 128, 129, 255, 300, 1000, 2049, 5000]))
+        cases.append((M, N, K, group))
+    return cases
+
+
+@pytest.mark.parametrize("case", _seeded_shapes())
+def test_seeded_shape_walk(btm, oracle, case):
+    M, N, K, group = case
+    w, packed, s, act = make(M, N, K, group, 101 + M + N + K)
+    out = gpu_matmul(btm, act, packed, s, group)
+    assert not np.isnan(out).any()
+    btm.check_device_status(0)
+    ref = oracle.int4_matmul(act.view(np.uint16), packed, s.view(np.uint16), group)
+    assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, ref) <= 2e-3
