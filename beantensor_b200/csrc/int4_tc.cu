@@ -10,28 +10,29 @@
 // N = 11008) and divides the activation bytes a CTA pulls from L2 by the same factor; the partial
 // accumulators meet in the shared memory of the cluster's first CTA.
 //
-// Roles in a CTA (7 warps), per 128-k unit of its K slice:
-//   warp 0      TMA: packed weights, 128 rows x 64 B (64-byte swizzle), ring of 3-4 units;
+// Roles in a CTA (11 warps), per 128-k unit of its K slice:
+//   warp 0      TMA: packed weights, 128 rows x 64 B (64-byte swizzle), ring of 4-6 units;
 //   warp 2      TMA: activation tiles, MB rows x 64 k (K-major, 128-byte swizzle), two per unit;
 //   warps 3-10  dequantise: thread = weight row, the two groups of four warps take alternate units; four
 //               128-bit shared loads, unpack to exact fp16 integers in natural k order, multiply by
 //               the group scale, and write the row's 128 fp16 straight into tensor memory (tcgen05.st,
-//               64 columns of the thread's own lane): the tensor core takes its A operand from there, so the tile never
-//               passes through shared memory and needs no proxy fence. Eight warps per CTA and two
-//               CTAs per SM: the dequantisation is the critical resource;
+//               64 columns of the thread's own lane): the tensor core takes its A operand from
+//               there, so the tile never passes through shared memory and needs no proxy fence. A
+//               warp passes one set of hand-offs per 128 k; those hand-offs, not arithmetic or
+//               bandwidth, are what the kernel's time is made of;
 //   warp 1      tcgen05.mma (M = 128, N = MB, A from tensor memory, B K-major in shared memory);
-//               tcgen05.commit frees the stages.
-// Then every CTA reads its accumulator (lane = weight row, column = activation row); CTAs 1.. of the
-// cluster store theirs into CTA 0's shared memory (column-major, so a warp writes 128 contiguous bytes),
-// and CTA 0 adds the partials in rank order, rounds once to fp16, transposes the tile through shared
-// memory and stores rows of 256 contiguous bytes of out[m, n0 .. n0 + 128).
+//               tcgen05.commit frees the activation tile after each 64-k block and the unit in
+//               tensor memory after both.
+// Then CTAs 1.. of the cluster park their accumulator (lane = weight row, column = activation row) in
+// their own shared memory, and after one cluster barrier CTA 0 fetches the parked values over DSMEM,
+// adds them to its own in rank order, rounds once to fp16, transposes the tile through shared memory
+// and stores rows of 256 contiguous bytes of out[m, n0 .. n0 + 128).
 // HBM traffic: the packed weights once (N*K/2 bytes) plus scales; activations come from L2
 // (N/128 x M x K x 2 bytes in total, whatever the split).
 #include <cuda_fp16.h>
 
 #include "btm_internal.h"
 #include "btm_ptx.cuh"
-#include "gemm_epilogue.cuh"
 
 namespace btm {
 
@@ -82,8 +83,8 @@ struct Cfg {
     static constexpr int W_STAGES = (TMEM_COLS - MB) / W_COLS; // 3 or 2 units in tensor memory
     static constexpr int ACT_BYTES = MB * 128;
     static constexpr int RING_BYTES = ACT_STAGES * ACT_BYTES + RAW_STAGES * RAW_BYTES;
-    // After the main loop the rings are dead and hold the other CTAs' partial accumulators and the output tile.
-    static_assert(OUT_TILE_OFF + RED_COLS * BW * 2 <= RING_BYTES, "reduction buffers must fit in the rings");
+    // After the main loop the rings are dead and hold the parked accumulator (MB x 128 fp32) or, in CTA 0, the output tile.
+    static_assert(OUT_TILE_OFF + RED_COLS * BW * 2 <= RING_BYTES && MB * BW * 4 <= RING_BYTES, "reduction buffers must fit in the rings");
     static constexpr int SMEM_BYTES = RING_BYTES + 1024; // + BW * groups-in-slice * 2 bytes of scales at run time
 };
 constexpr int SCALE_SMEM_MAX = 6144;
@@ -119,11 +120,6 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta)
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
     return r;
 }
-__device__ __forceinline__ void st_cluster_b32(uint32_t addr, uint32_t bits)
-{
-    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(addr), "r"(bits) : "memory");
-}
-
 template <int MB>
 __global__ void __launch_bounds__(i4tc::THREADS, 2)
 int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ CUtensorMap tmW, const GemmParams p,
@@ -325,45 +321,55 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     }
 
     // ---------------------------------------------------------------- split-K reduction and output
-    // Every thread of every CTA of the cluster passes the same cluster barriers, whatever happened above.
-    __syncthreads();    // this CTA's rings are dead: its tensor-core and TMA traffic is over
+    // Every thread of every CTA of the cluster passes the same two cluster barriers, whatever happened above.
+    __syncthreads(); // this CTA's rings are dead: its tensor-core and TMA traffic is over
     const bool acc_ok = abort_flag == 0; // the same answer in every thread of the CTA
-    cluster_sync_all(); // ... in every CTA of the cluster, so CTA 0's rings may now be overwritten
     const bool epi = warp >= 3;
-    const int quad = warp & 3;                 // the tensor-memory lanes this warp may read
-    const int erow = quad * 32 + lane;         // accumulator lane = weight row of the tile
-    const int chalf = (warp - 3) >> 2;         // which 32 of a round's 64 columns
-    const uint32_t red0 = map_to_cta(smem_base, 0);
-    const float *red = reinterpret_cast<const float *>(smem_al);
-    uint16_t *tile_out = reinterpret_cast<uint16_t *>(smem_al + OUT_TILE_OFF);
-    uint16_t *out = reinterpret_cast<uint16_t *>(p.C[0]);
-    const bool vec_store = (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    const int quad = warp & 3;         // the tensor-memory lanes this warp may read
+    const int erow = quad * 32 + lane; // accumulator lane = weight row of the tile
+    const int chalf = (warp - 3) >> 2; // which 32 of a round's 64 columns
+    float *park = reinterpret_cast<float *>(smem_al); // [MB columns][128 rows] fp32 over the dead rings
+    // CTAs 1.. park their accumulator in their own shared memory (column-major: a warp writes 128 contiguous
+    // bytes); CTA 0 fetches it from there after the barrier. Nothing is written into another CTA's memory, so
+    // no CTA has to wait for another one's main loop before it may start.
+    if (epi && crank != 0) {
 #pragma unroll 1
-    for (int h = 0; h < MB / RED_COLS; ++h) {
-        uint32_t v[32];
-        if (epi) {
-            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * RED_COLS + chalf * 32), v);
+        for (int h = 0; h < MB / RED_COLS; ++h) {
+            uint32_t v[32];
+            const int col0 = h * RED_COLS + chalf * 32;
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, v);
             tmem_ld_wait();
-            if (crank != 0 && acc_ok) {
-                const uint32_t dst = red0 + (crank - 1) * RED_BYTES + (uint32_t)(chalf * 32 * BW + erow) * 4u;
 #pragma unroll
-                for (int c = 0; c < 32; ++c) st_cluster_b32(dst + (uint32_t)c * (BW * 4), v[c]);
-            }
+            for (int c = 0; c < 32; ++c) park[(col0 + c) * BW + erow] = __uint_as_float(v[c]);
         }
-        cluster_sync_all(); // partials of this round are in CTA 0's shared memory
-        if (epi && crank == 0 && acc_ok) {
+    }
+    cluster_sync_all(); // every accumulator of the cluster is parked and visible (release / acquire)
+    if (epi && crank == 0 && acc_ok) {
+        uint16_t *tile_out = reinterpret_cast<uint16_t *>(smem_al + OUT_TILE_OFF);
+        uint16_t *out = reinterpret_cast<uint16_t *>(p.C[0]);
+        const bool vec_store = (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+#pragma unroll 1
+        for (int h = 0; h < MB / RED_COLS; ++h) {
+            uint32_t v[32];
+            const int col0 = h * RED_COLS + chalf * 32;
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, v);
+            tmem_ld_wait();
             float acc[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) acc[c] = __uint_as_float(v[c]);
 #pragma unroll
-            for (int r = 1; r < MAX_SPLIT; ++r) {
+            for (int r = 1; r < MAX_SPLIT; ++r) { // rank order: the sum does not depend on timing
                 if (r < (int)csize) {
-                    const float *src = red + (r - 1) * RED_FLOATS + chalf * 32 * BW + erow;
+                    const uint32_t src = map_to_cta(smem_base + (uint32_t)(col0 * BW + erow) * 4u, (uint32_t)r);
+                    float x[32];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) acc[c] += src[c * BW];
+                    for (int c = 0; c < 32; ++c) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x[c]) : "r"(src + (uint32_t)c * (BW * 4)));
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) acc[c] += x[c];
                 }
             }
             // fp16 tile [64 m][128 n] in shared memory, then rows of 256 contiguous bytes to global memory
+            if (h > 0) asm volatile("bar.sync 1, 256;" ::: "memory"); // the previous round's tile has been read
 #pragma unroll
             for (int c = 0; c < 32; ++c) tile_out[(chalf * 32 + c) * BW + erow] = __half_as_ushort(__float2half_rn(acc[c]));
             asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -386,8 +392,8 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
                 }
             }
         }
-        if (h + 1 < MB / RED_COLS) cluster_sync_all(); // CTA 0 has consumed the round: the buffers may be rewritten
     }
+    cluster_sync_all(); // CTA 0 has read the parked accumulators: their owners may exit
 
     tc_fence_before();
     __syncthreads();
