@@ -173,7 +173,13 @@ int btm_bmm(int device, void *stream, int dtype, int batch, int M, int N, int K,
  * W packed two nibbles per byte along K ([N, K/2] bytes) and one fp16 scale per `group`
  * consecutive k ([N, K/group]). The dtype is this build's addition to Tensor/Dtypes.h:57-70.
  * Arithmetic: fp32 accumulation of act*w inside a group, times the scale, summed over
- * groups, rounded to nearest even. K % group == 0, group % 32 == 0, K % 32 == 0. */
+ * groups, rounded to nearest even (for M > 8 the weights are first rounded to fp16 as
+ * btm_int4_dequant defines them and the product accumulates in fp32). K % group == 0,
+ * group % 32 == 0, K % 32 == 0.
+ * Ordering: products with M <= 8 use programmatic dependent launch. If the preceding kernel on the
+ * stream is another such product, this one may read w_packed and scales_f16 while that kernel is
+ * still running (act_f16 is read and out_f16 written only after it has completed); w_packed and
+ * scales_f16 must therefore not be the output of an immediately preceding M <= 8 product. */
 int btm_int4_matmul(int device, void *stream, int M, int N, int K, int group, const void *act_f16,
                     const void *w_packed, const void *scales_f16, void *out_f16);
 
