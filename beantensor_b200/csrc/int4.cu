@@ -277,6 +277,22 @@ int4_gemv_kernel(const __grid_constant__ CUtensorMap tmW, int M, int N, int K, i
     }
 }
 
+// Shared-memory loads by 32-bit shared address with a compile-time byte offset: the inner loop of the streaming
+// GEMV keeps one running address per operand and lets the offsets ride in the instruction.
+template <int kOff>
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(kOff));
+    return v;
+}
+__device__ __forceinline__ float lds_f16(uint32_t addr)
+{
+    unsigned short h;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
+    return __half2float(__ushort_as_half(h));
+}
+
 // Streaming GEMV for M <= 8: one persistent CTA per SM walks the 16-row weight blocks c, c + grid, ... and
 // keeps the weight stream running while it computes. A block's 16 rows are consecutive in memory (16 * K/2
 // bytes, and its scales one span of 16 * G halves); a producer warp brings them in with bulk copies (one per
@@ -385,8 +401,11 @@ int4_gemv_stream_kernel(const uint8_t *__restrict__ w, int M, int N, int K, int 
         // so their lanes load nothing (a shared-memory access with four active lanes is one wavefront, not four).
         const bool has_row = g < mrows;
         const uint4 *arow = reinterpret_cast<const uint4 *>(act + (size_t)min(g, mrows - 1) * K) + t * 4;
-        const uint4 *arow_s = act_s + min(g, mrows - 1) * act_pitch + t * 4;
+        const uint32_t act_u32 = smem_u32(act_s) + (uint32_t)((min(g, mrows - 1) * act_pitch + t * 4 + kb_lo * 16) * 16);
         const int bpg = group / 128;
+        const uint32_t rowB_off = 8u * (uint32_t)row_pitch, sB_off = 16u * (uint32_t)G; // rows g + 8: weights, scales
+        // Activation words of the lanes without a row stay zero for the whole kernel.
+        uint4 av[4] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
 
 #pragma unroll 1
         for (int bi = 0; bi < my_blocks; ++bi) {
@@ -394,46 +413,52 @@ int4_gemv_stream_kernel(const uint8_t *__restrict__ w, int M, int N, int K, int 
             const int n0 = ((int)blockIdx.x + bi * (int)gridDim.x) * GEMV_ROWS;
             float tot[4] = {0.f, 0.f, 0.f, 0.f};
             if (!mbar_wait_warp(smem_u32(&bar_full[stage]), (uint32_t)((bi / GS_STAGES) & 1), &abort_flag, status, WAIT_EPI_STAGE)) break;
-            const uint8_t *st_base = wsm + (size_t)stage * stage_bytes;
-            const uint8_t *rowA = st_base + (size_t)g * row_pitch + t * 16;
-            const uint8_t *rowB = rowA + 8 * (size_t)row_pitch;
-            const __half *sA = reinterpret_cast<const __half *>(st_base + w_bytes) + g * G;
-            const __half *sB = sA + 8 * G;
+            const uint32_t st_u32 = smem_u32(wsm) + (uint32_t)stage * (uint32_t)stage_bytes;
+            uint32_t aW = st_u32 + (uint32_t)(g * row_pitch + t * 16 + kb_lo * 64);              // row g, this lane's 16 bytes of block kb
+            const uint32_t aS0 = st_u32 + (uint32_t)w_bytes + (uint32_t)(g * G) * 2u;             // row g's scales
+            uint32_t aA = act_u32;
 #pragma unroll 1
-            for (int kb = kb_lo; kb < kb_hi; ++kb) {
-                const uint4 qa = *reinterpret_cast<const uint4 *>(rowA + kb * 64);
-                const uint4 qb = *reinterpret_cast<const uint4 *>(rowB + kb * 64);
+            for (int kb = kb_lo; kb < kb_hi; ++kb, aW += 64u, aA += 256u) {
+                const uint4 qa = lds128<0>(aW);
+                const uint4 qb = lds128<0>(aW + rowB_off);
                 const uint32_t xa[4] = {qa.x, qa.y, qa.z, qa.w};
                 const uint32_t xb[4] = {qb.x, qb.y, qb.z, qb.w};
-                const int si = bpg == 1 ? kb : (int)((unsigned)kb / (unsigned)bpg);
-                const float sa = __half2float(sA[si]);
-                const float sb = __half2float(sB[si]);
-                {
-                    float c0[4], c1[4];
+                const uint32_t aS = aS0 + 2u * (uint32_t)(bpg == 1 ? kb : (int)((unsigned)kb / (unsigned)bpg));
+                const float sa = lds_f16(aS);
+                const float sb = lds_f16(aS + sB_off);
+                if (has_row) {
+                    if constexpr (kStageAct) {
+                        av[0] = lds128<0>(aA);
+                        av[1] = lds128<16>(aA);
+                        av[2] = lds128<32>(aA);
+                        av[3] = lds128<48>(aA);
+                    } else {
 #pragma unroll
-                    for (int wd = 0; wd < 4; ++wd) {
-                        uint4 av = make_uint4(0u, 0u, 0u, 0u);
-                        if (has_row) av = kStageAct ? arow_s[kb * 16 + wd] : __ldg(arow + kb * 16 + wd);
-                        uint32_t ha[4], hb[4];
-                        unpack8(xa[wd], ha);
-                        unpack8(xb[wd], hb);
-                        const uint32_t b04 = kStageAct ? av.x : __byte_perm(av.x, av.z, 0x5410);
-                        const uint32_t b15 = kStageAct ? av.y : __byte_perm(av.x, av.z, 0x7632);
-                        const uint32_t b26 = kStageAct ? av.z : __byte_perm(av.y, av.w, 0x5410);
-                        const uint32_t b37 = kStageAct ? av.w : __byte_perm(av.y, av.w, 0x7632);
-                        if (wd == 0) {
-                            mma_16816_first(c0, ha[0], hb[0], ha[1], hb[1], b04, b15);
-                            mma_16816_first(c1, ha[2], hb[2], ha[3], hb[3], b26, b37);
-                        } else {
-                            mma_16816(c0, ha[0], hb[0], ha[1], hb[1], b04, b15);
-                            mma_16816(c1, ha[2], hb[2], ha[3], hb[3], b26, b37);
-                        }
+                        for (int wd = 0; wd < 4; ++wd) av[wd] = __ldg(arow + kb * 16 + wd);
                     }
-                    tot[0] = fmaf(sa, c0[0] + c1[0], tot[0]);
-                    tot[1] = fmaf(sa, c0[1] + c1[1], tot[1]);
-                    tot[2] = fmaf(sb, c0[2] + c1[2], tot[2]);
-                    tot[3] = fmaf(sb, c0[3] + c1[3], tot[3]);
                 }
+                float c0[4], c1[4];
+#pragma unroll
+                for (int wd = 0; wd < 4; ++wd) {
+                    uint32_t ha[4], hb[4];
+                    unpack8(xa[wd], ha);
+                    unpack8(xb[wd], hb);
+                    const uint32_t b04 = kStageAct ? av[wd].x : __byte_perm(av[wd].x, av[wd].z, 0x5410);
+                    const uint32_t b15 = kStageAct ? av[wd].y : __byte_perm(av[wd].x, av[wd].z, 0x7632);
+                    const uint32_t b26 = kStageAct ? av[wd].z : __byte_perm(av[wd].y, av[wd].w, 0x5410);
+                    const uint32_t b37 = kStageAct ? av[wd].w : __byte_perm(av[wd].y, av[wd].w, 0x7632);
+                    if (wd == 0) {
+                        mma_16816_first(c0, ha[0], hb[0], ha[1], hb[1], b04, b15);
+                        mma_16816_first(c1, ha[2], hb[2], ha[3], hb[3], b26, b37);
+                    } else {
+                        mma_16816(c0, ha[0], hb[0], ha[1], hb[1], b04, b15);
+                        mma_16816(c1, ha[2], hb[2], ha[3], hb[3], b26, b37);
+                    }
+                }
+                tot[0] = fmaf(sa, c0[0] + c1[0], tot[0]);
+                tot[1] = fmaf(sa, c0[1] + c1[1], tot[1]);
+                tot[2] = fmaf(sb, c0[2] + c1[2], tot[2]);
+                tot[3] = fmaf(sb, c0[3] + c1[3], tot[3]);
             }
             // This warp's words and scales of the stage are consumed: hand the stage back.
             __syncwarp();
