@@ -301,7 +301,7 @@ __device__ __forceinline__ float lds_f16(uint32_t addr)
 // own an eighth of K of every block and never meet on a CTA-wide barrier: a warp writes its partial sums,
 // counts itself in, and the warp that arrives last adds the partials in warp order (so the result does not
 // depend on arrival order) and stores the block's outputs.
-// The CTA uses less than half of an SM's shared memory and registers, and the grid is launched with
+// For M <= 4 the CTA uses less than half of an SM's shared memory and registers, and the grid is launched with
 // programmatic stream serialisation: the next int4 launch on the stream becomes resident beside this one
 // and streams its first blocks (weights and scales are parameters no predecessor writes) while this one is
 // still computing; its computing warps touch the activations only after griddepcontrol.wait. Back-to-back
@@ -393,7 +393,7 @@ int4_gemv_stream_kernel(const uint8_t *__restrict__ w, int M, int N, int K, int 
                 o.y = __byte_perm(r.x, r.z, 0x7632);
                 o.z = __byte_perm(r.y, r.w, 0x5410);
                 o.w = __byte_perm(r.y, r.w, 0x7632);
-                act_s[i + (i >= K / 8 ? 1 : 0)] = o; // at most two staged rows
+                act_s[i + i / (K / 8)] = o; // row pitch K/8 + 1: one pad word per row
             }
             asm volatile("bar.sync 1, 256;" ::: "memory"); // the computing warps' own barrier (GS_WARPS * 32 threads), once
         }
@@ -761,8 +761,8 @@ static int grid_for(long long items, int block, int sm_cap)
 
 int configure_int4_gemv_kernels()
 {
-    cudaError_t e = cudaFuncSetAttribute(int4_gemv_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(int4_gemv_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(int4_gemv_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 150 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(int4_gemv_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 150 * 1024);
     return check_cuda(e, "cudaFuncSetAttribute(int4_gemv_stream)");
 }
 
@@ -805,19 +805,25 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
         if (rc) return rc;
         return check_cuda(cudaGetLastError(), "int4 gemm launch");
     }
-    const bool stage_act = M <= 2;
+    const bool stage_act = M <= 2; // slab kernel: a slab and more than two staged rows do not fit together
     const int npieces = (K / 128 + 1) / 2;
     // Streaming kernel: K long enough to give each of its eight warps a 128-k block, a block's scales a whole
-    // number of 16-byte units at a 16-byte-aligned address, and two stages plus the partial sums and the staged
-    // activations within half an SM's shared memory.
+    // number of 16-byte units at a 16-byte-aligned address, and two stages plus the partial sums within its shared
+    // memory budget. The activations are staged beside them when that still fits: up to 110 KB in all for M <= 4
+    // (the next launch then fits on the SM beside this one), up to 150 KB for more rows (13.1 -> 10.9 us at M = 8:
+    // the permuted copy takes four global loads and eight byte-permutes per 128-k block out of the inner loop,
+    // which is worth more there than the early residency of the successor).
     const char *force_gemv = getenv("BTM_FORCE_GEMV");
     const int mrows_s = M < 8 ? M : 8;
-    const size_t smem_stream = (size_t)GS_STAGES * GEMV_ROWS * (K / 2 + ((192 - ((K / 2) & 127)) & 127) + (K / group) * 2) + (((size_t)GS_RED * GS_WARPS * 16 * mrows_s * 4 + 15) & ~(size_t)15) +
-                               (stage_act ? (size_t)M * (K / 8 + 1) * sizeof(uint4) : 0);
+    const size_t smem_base_s = (size_t)GS_STAGES * GEMV_ROWS * (K / 2 + ((192 - ((K / 2) & 127)) & 127) + (K / group) * 2) +
+                               (((size_t)GS_RED * GS_WARPS * 16 * mrows_s * 4 + 15) & ~(size_t)15);
+    const size_t smem_staged = smem_base_s + (size_t)M * (K / 8 + 1) * sizeof(uint4);
+    const bool stage_act_stream = smem_staged <= (size_t)(M <= 4 ? 110 : 150) * 1024;
+    const size_t smem_stream = stage_act_stream ? smem_staged : smem_base_s;
     const bool stream_ok = K / 128 >= GS_WARPS && (K / 2) % 16 == 0 && (K / group) % 8 == 0 && (((uintptr_t)scales & 15) == 0) &&
-                           smem_stream <= 100 * 1024 && !(force_gemv && !strcmp(force_gemv, "slab"));
+                           smem_stream <= 150 * 1024 && !(force_gemv && !strcmp(force_gemv, "slab"));
     if (stream_ok) {
-        const void *fn = stage_act ? (const void *)int4_gemv_stream_kernel<true> : (const void *)int4_gemv_stream_kernel<false>;
+        const void *fn = stage_act_stream ? (const void *)int4_gemv_stream_kernel<true> : (const void *)int4_gemv_stream_kernel<false>;
         const int nblocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(nblocks < sm_count ? nblocks : sm_count));
