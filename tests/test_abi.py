@@ -48,6 +48,12 @@ def test_argument_errors_precede_device_work():
     assert rc == _lib.ERR_INVALID
     rc = L.btm_bmm(0, None, _lib.F32, 1, 4, 4, 4, None, 16, None, 16, None, 16)
     assert rc == _lib.ERR_UNSUPPORTED
+    # fused epilogue: an unknown activation code is refused before any device work
+    p = ctypes.c_void_p(16)
+    rc = L.btm_gemm_bias_act(0, None, _lib.F16, 4, 4, 4, p, 4, p, 4, None, 7, p, 4)
+    assert rc == _lib.ERR_INVALID and b"activation" in L.btm_last_error_string()
+    rc = L.btm_gemm_bias_act(0, None, _lib.I32, 4, 4, 4, p, 4, p, 4, None, 1, p, 4)
+    assert rc == _lib.ERR_UNSUPPORTED
 
 
 def test_no_cpu_fallback_without_device():
