@@ -42,6 +42,18 @@ int main()
         try { btm_raise(BTM_ERR_CUDA); } catch (const std::runtime_error &) { ++passed; }
         btm_raise(BTM_OK);
     }
+    {   // fused epilogue: a bias of the wrong length is refused by the binding's own guard
+        auto a = view(BTM_F16, 1, 4, 4), b = view(BTM_F16, 1, 4, 4), o = view(BTM_F16, 1, 4, 4);
+        btm_tensor_view bias;
+        std::memset(&bias, 0, sizeof(bias));
+        bias.data = reinterpret_cast<void *>(0x1000);
+        bias.dtype = BTM_F16;
+        bias.device = 1;
+        bias.ndim = 1;
+        bias.shape[0] = 5;
+        bias.strides[0] = 1;
+        try { matmul_bias_act_gpu(a, b, &bias, true, o); } catch (const std::invalid_argument &) { ++passed; }
+    }
     std::printf("passed=%d\n", passed);
-    return passed == 5 ? 0 : 1;
+    return passed == 6 ? 0 : 1;
 }

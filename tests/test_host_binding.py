@@ -23,4 +23,4 @@ def test_cpp_binding_compiles_and_maps_errors(tmp_path):
     subprocess.check_call(cmd)
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert "passed=5" in r.stdout
+    assert "passed=6" in r.stdout
