@@ -160,6 +160,23 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         return u + u0;
     };
 
+    // The dequantising warps ask for their slice's scales before anything else happens in the CTA: once the weight
+    // ring's first loads are queued (a dozen megabytes over the whole grid) a small load comes back microseconds
+    // later, and no weight can be dequantised before the scales are there.
+    constexpr int SC_PRE = 6; // per-thread prefetch depth; the rest (long K or small groups) is fetched afterwards
+    __half sc_pre[SC_PRE];
+    const int sc_total = BW * g_cnt, G = p.K / group;
+    if (warp >= 3) {
+#pragma unroll
+        for (int j = 0; j < SC_PRE; ++j) {
+            const int i = (int)threadIdx.x - DQ_FIRST + j * 256;
+            if (i < sc_total) {
+                const int r = i / g_cnt, g = i - r * g_cnt;
+                sc_pre[j] = __ldg(scales + (size_t)min(n0 + r, p.N - 1) * G + g_first + g);
+            }
+        }
+    }
+
     if (warp == 0 && lane == 0) {
         abort_flag = 0;
         for (int i = 0; i < RAW_STAGES; ++i) {
@@ -261,10 +278,13 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         // A thread's row is the tensor-memory lane its warp may write: quadrant warp % 4.
         const int dq = threadIdx.x - DQ_FIRST; // 0..255
         const int grp = (warp - 3) >> 2, row = (warp & 3) * 32 + lane;
-        // The eight warps fetch the slice's scales together, right away (a load issued once the weight
-        // stream is queued would come back last), and meet on a named barrier of their own.
-        const int G = p.K / group;
-        for (int i = dq; i < BW * g_cnt; i += 256) {
+        // The prefetched scales go to shared memory; the eight warps meet on a named barrier of their own.
+#pragma unroll
+        for (int j = 0; j < SC_PRE; ++j) {
+            const int i = dq + j * 256;
+            if (i < sc_total) sc_s[i] = sc_pre[j];
+        }
+        for (int i = dq + SC_PRE * 256; i < sc_total; i += 256) {
             const int r = i / g_cnt, g = i - r * g_cnt;
             sc_s[i] = __ldg(scales + (size_t)min(n0 + r, p.N - 1) * G + g_first + g);
         }
