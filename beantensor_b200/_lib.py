@@ -20,6 +20,7 @@ SIGNATURES = {
     "btm_dtype_size": (_sz, [_i]),
     "btm_version": (_i, []),
     "btm_last_error_string": (C.c_char_p, []),
+    "btm_debug_set": (_i, [C.c_char_p, C.c_longlong]),
     "btm_init": (_i, [_i]),
     "btm_check_device_status": (_i, [_i, _vp]),
     "btm_gemm": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
@@ -35,6 +36,7 @@ SIGNATURES = {
     "btm_convert": (_i, [_i, _vp, _i, _i, _i64, _vp, _vp]),
     "btm_int4_unpack": (_i, [_i, _vp, _i, _i, _vp, _vp]),
     "btm_gemm_nshard": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, C.POINTER(_vp), _i64, _i, _i]),
+    "btm_replicate_rows": (_i, [_i, _vp, C.POINTER(_vp), _i, _i, _sz, _sz]),
     "btm_ipc_alloc": (_i, [_i, _sz, C.POINTER(_vp), C.c_char_p]),
     "btm_ipc_open": (_i, [_i, C.c_char_p, C.POINTER(_vp)]),
     "btm_ipc_close": (_i, [_i, _vp]),

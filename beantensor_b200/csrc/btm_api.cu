@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <algorithm>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "btm_internal.h"
@@ -34,6 +35,17 @@ int check_cuda(cudaError_t e, const char *what)
     return set_error(BTM_ERR_CUDA, "CUDA Error: %s (%s)", cudaGetErrorString(e), what);
 }
 
+// Test hooks (btm_debug_set): process-wide, read at every launch.
+static std::atomic<long long> g_dbg_wait_limit{0};
+static std::atomic<int> g_dbg_skip_loads{0};
+
+void fill_wait_params(GemmParams *p)
+{
+    const long long lim = g_dbg_wait_limit.load(std::memory_order_relaxed);
+    p->wait_limit = lim > 0 ? lim : 2000000000LL; // about one second of SM clocks; the longest kernel here runs milliseconds
+    p->debug_skip_loads = g_dbg_skip_loads.load(std::memory_order_relaxed);
+}
+
 constexpr int kMaxDevices = 64;
 static DeviceState g_dev[kMaxDevices];
 static std::mutex g_dev_mu;
@@ -41,13 +53,33 @@ static std::mutex g_dev_mu;
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn g_encode = nullptr;
+static std::atomic<EncodeTiledFn> g_encode{nullptr};
+
+// Looks the driver's tensor-map encoder up once per process. Allocates nothing.
+static int ensure_encode()
+{
+    if (g_encode.load(std::memory_order_acquire)) return BTM_OK;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    int rc = check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint");
+    if (rc) return rc;
+    if (qres != cudaDriverEntryPointSuccess || !fn) return set_error(BTM_ERR_CUDA, "CUDA Error: driver does not export cuTensorMapEncodeTiled");
+    g_encode.store((EncodeTiledFn)fn, std::memory_order_release);
+    return BTM_OK;
+}
 
 DeviceState *device_state(int device)
 {
     if (device < 0 || device >= kMaxDevices) {
         set_error(BTM_ERR_INVALID, "Invalid GPU ID %d", device);
         return nullptr;
+    }
+    DeviceState *ds = &g_dev[device];
+    // Ready path: no lock and no device query, only the switch of the calling thread's current device (the
+    // reference's pool threads arrive with whatever device they used last).
+    if (ds->ready.load(std::memory_order_acquire)) {
+        if (check_cuda(cudaSetDevice(device), "cudaSetDevice")) return nullptr;
+        return ds;
     }
     int count = 0;
     if (check_cuda(cudaGetDeviceCount(&count), "cudaGetDeviceCount")) return nullptr;
@@ -56,9 +88,8 @@ DeviceState *device_state(int device)
         return nullptr;
     }
     if (check_cuda(cudaSetDevice(device), "cudaSetDevice")) return nullptr;
-    DeviceState *ds = &g_dev[device];
     std::lock_guard<std::mutex> lock(g_dev_mu);
-    if (ds->ready) return ds;
+    if (ds->ready.load(std::memory_order_acquire)) return ds;
     cudaDeviceProp prop;
     if (check_cuda(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties")) return nullptr;
     if (prop.major != 10) {
@@ -66,27 +97,27 @@ DeviceState *device_state(int device)
                   prop.minor);
         return nullptr;
     }
-    if (!g_encode) {
-        void *fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint"))
-            return nullptr;
-        if (qres != cudaDriverEntryPointSuccess || !fn) {
-            set_error(BTM_ERR_CUDA, "CUDA Error: driver does not export cuTensorMapEncodeTiled");
-            return nullptr;
-        }
-        g_encode = (EncodeTiledFn)fn;
-    }
+    if (ensure_encode()) return nullptr;
     if (check_cuda(cudaMalloc(&ds->status, sizeof(int)), "cudaMalloc(status)")) return nullptr;
     if (check_cuda(cudaMemset(ds->status, 0, sizeof(int)), "cudaMemset(status)")) return nullptr;
+    // Scratch of the fp32 product comes from a pool of this library's own, in stream order. The release
+    // threshold keeps freed blocks in the pool, so that after the first call of a shape an allocation is a
+    // bookkeeping step on the host and not a trip to the driver.
+    cudaMemPoolProps props;
+    memset(&props, 0, sizeof(props));
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = device;
+    if (check_cuda(cudaMemPoolCreate(&ds->pool, &props), "cudaMemPoolCreate")) return nullptr;
+    unsigned long long keep = ~0ull;
+    if (check_cuda(cudaMemPoolSetAttribute(ds->pool, cudaMemPoolAttrReleaseThreshold, &keep), "cudaMemPoolSetAttribute")) return nullptr;
     if (configure_gemm_tc_kernels()) return nullptr;
     if (configure_gemm_tc2_kernels()) return nullptr;
     if (configure_int4_tc_kernels()) return nullptr;
     if (configure_int4_gemv_kernels()) return nullptr;
     ds->sm_count = prop.multiProcessorCount;
-    ds->ws = nullptr;
-    ds->ws_bytes = 0;
-    ds->ready = true;
+    ds->ready.store(true, std::memory_order_release);
     return ds;
 }
 
@@ -101,7 +132,8 @@ int encode_tmap_3d(CUtensorMap *out, int dtype, const void *base, uint64_t d0, u
     cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
     cuuint32_t box[3] = {box0, box1, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode(out, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    if (int rc = ensure_encode()) return rc;
+    CUresult r = g_encode.load(std::memory_order_acquire)(out, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -187,6 +219,7 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
     p.col0 = c.col0;
     p.c_vec_ok = vec ? 1 : 0;
     p.status = ds->status;
+    fill_wait_params(&p);
     p.bias = c.bias;
     p.act = c.act;
     if (c.ndst > 1) {
@@ -250,6 +283,7 @@ static int run_f32(DeviceState *ds, cudaStream_t st, const GemmCall &c, void *ws
     p.ldc = c.ldc;
     p.c_vec_ok = (aligned16(c.C[0]) && (c.ldc * 4) % 16 == 0) ? 1 : 0;
     p.status = ds->status;
+    fill_wait_params(&p);
     p.bias = c.bias;
     p.act = c.act;
     StoreMaps cm;
@@ -294,6 +328,21 @@ size_t btm_dtype_size(int dtype)
 
 int btm_version(void) { return 100; }
 
+int btm_debug_set(const char *key, long long value)
+{
+    if (!key) return set_error(BTM_ERR_INVALID, "debug switch: null key");
+    if (!strcmp(key, "wait_limit_cycles")) {
+        if (value < 0) return set_error(BTM_ERR_INVALID, "debug switch wait_limit_cycles: negative value");
+        g_dbg_wait_limit.store(value);
+        return BTM_OK;
+    }
+    if (!strcmp(key, "skip_loads")) {
+        g_dbg_skip_loads.store(value ? 1 : 0);
+        return BTM_OK;
+    }
+    return set_error(BTM_ERR_INVALID, "debug switch: unknown key '%s'", key);
+}
+
 const char *btm_last_error_string(void) { return g_err; }
 
 int btm_init(int device) { return device_state(device) ? BTM_OK : last_code(); }
@@ -332,22 +381,17 @@ static int gemm_entry(int device, void *stream, int dtype, int M, int N, int K, 
     c.C[0] = C; c.ndst = 1; c.ldc = ldc;
     c.bias = bias; c.act = act;
     if (dtype != BTM_F32) return run_16bit(ds, st, c);
+    // fp32: the operand planes live in scratch that belongs to this call alone. It is taken from the library's pool
+    // and given back in stream order on the caller's stream, so calls on other streams or threads never see it and
+    // nothing is freed under work that is still queued.
     const size_t need = btm_gemm_f32_workspace_bytes(M, N, K);
-    {
-        std::lock_guard<std::mutex> lock(g_dev_mu);
-        if (ds->ws_bytes < need) {
-            // Growing the scratch must not pull memory from under work already queued.
-            rc = check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
-            if (rc) return rc;
-            if (ds->ws) cudaFree(ds->ws);
-            ds->ws = nullptr;
-            ds->ws_bytes = 0;
-            rc = check_cuda(cudaMalloc(&ds->ws, need), "cudaMalloc(fp32 split scratch)");
-            if (rc) return rc;
-            ds->ws_bytes = need;
-        }
-    }
-    return run_f32(ds, st, c, ds->ws, ds->ws_bytes);
+    if (need == 0) return run_f32(ds, st, c, nullptr, 0);
+    void *ws = nullptr;
+    rc = check_cuda(cudaMallocFromPoolAsync(&ws, need, ds->pool, st), "cudaMallocFromPoolAsync(fp32 split scratch)");
+    if (rc) return rc;
+    rc = run_f32(ds, st, c, ws, need);
+    const int rc_free = check_cuda(cudaFreeAsync(ws, st), "cudaFreeAsync(fp32 split scratch)");
+    return rc ? rc : rc_free;
 }
 
 int btm_gemm(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *B, int64_t ldb,
@@ -437,6 +481,7 @@ int btm_gemm_bt(int device, void *stream, int dtype, int M, int N, int K, const 
     p.C[0] = C; p.ldc = ldc;
     p.c_vec_ok = (aligned16(C) && (ldc * (long long)es) % 16 == 0) ? 1 : 0;
     p.status = ds->status;
+    fill_wait_params(&p);
     StoreMaps cm;
     rc = encode_store_maps(&cm, dtype, p);
     if (rc) return rc;
@@ -531,6 +576,26 @@ int btm_int4_quantize(int device, void *stream, int N, int K, int group, const v
     DeviceState *ds = device_state(device);
     if (!ds) return last_code();
     return launch_int4_quantize((cudaStream_t)stream, N, K, group, w_f16, out_packed, out_scales_f16);
+}
+
+int btm_replicate_rows(int device, void *stream, void *const *bufs, int rank, int nranks, size_t offset_bytes, size_t bytes)
+{
+    if (nranks < 1 || nranks > kMaxDst || rank < 0 || rank >= nranks)
+        return set_error(BTM_ERR_INVALID, "replicate: rank %d of %d is out of range (at most %d ranks)", rank, nranks, kMaxDst);
+    if (!bufs) return set_error(BTM_ERR_INVALID, "replicate: null buffer table");
+    for (int r = 0; r < nranks; ++r)
+        if (!bufs[r]) return set_error(BTM_ERR_INVALID, "replicate: null buffer for rank %d", r);
+    if (!device_state(device)) return last_code();
+    if (bytes == 0) return BTM_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const char *src = (const char *)bufs[rank] + offset_bytes;
+    // One copy per peer, starting with the next rank so that the ranks do not all write into the same peer first.
+    for (int i = 1; i < nranks; ++i) {
+        char *dst = (char *)bufs[(rank + i) % nranks] + offset_bytes;
+        int rc = check_cuda(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st), "cudaMemcpyAsync(peer)");
+        if (rc) return rc;
+    }
+    return BTM_OK;
 }
 
 int btm_ipc_alloc(int device, size_t bytes, void **ptr, unsigned char handle[64])

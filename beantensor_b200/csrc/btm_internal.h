@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/btm.h"
 
 namespace btm {
@@ -29,6 +31,8 @@ struct GemmParams {
     int act;           // 0 none, 1 ReLU (after the bias)
     int c_vec_ok;      // 16-byte vector stores into C are legal
     int *status;       // device status word (bounded waits report here)
+    long long wait_limit; // SM cycles after which a wait inside the kernel gives up (set by fill_wait_params)
+    int debug_skip_loads; // test hook: the producer warps issue no loads, so the consumers' waits run out
 };
 
 // Output tensor maps of the epilogue's TMA stores, one per destination copy of C (local first, then peers).
@@ -38,14 +42,15 @@ struct StoreMaps {
 
 // Per-device state, created once by btm_init.
 struct DeviceState {
-    bool ready;
+    std::atomic<bool> ready;
     int sm_count;
-    int *status; // device memory, one int
-    void *ws;    // library-owned scratch for the fp32 split
-    size_t ws_bytes;
+    int *status;        // device memory, one int
+    cudaMemPool_t pool; // scratch of the fp32 split: allocated and freed in stream order, one block per call
 };
 
 int set_error(int code, const char *fmt, ...);
+// Sets p->wait_limit (the default of about one second, or what btm_debug_set installed) and the test hook.
+void fill_wait_params(GemmParams *p);
 int check_cuda(cudaError_t e, const char *what);
 DeviceState *device_state(int device); // NULL + error set on failure
 
@@ -78,6 +83,11 @@ int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once pe
 int configure_gemm_tc2_kernels();
 int configure_int4_tc_kernels();
 int configure_int4_gemv_kernels();
+int configure_int4_gemv_rows_kernels();
+// Register-resident GEMV (M <= 8). Returns a btm_status, or -1 when the shape is outside what it takes (nothing launched).
+// nb: 128-k blocks per warp, 16 (ten warps per CTA) or 8 (twenty).
+int launch_int4_gemv_rows(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
+                          const void *scales, void *out, int nb);
 int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const void *act, const void *w, const void *scales, void *out,
                         int *status, int sm_count);
 int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,

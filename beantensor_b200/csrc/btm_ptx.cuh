@@ -132,14 +132,15 @@ __device__ __forceinline__ bool mbar_wait_short_warp(uint32_t bar, uint32_t pari
 // Bounded wait. `abort_flag` is a CTA-shared int that any role raises when its own wait
 // ran out; every other waiter then gives up at once instead of running out its own clock.
 template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                          long long limit_cycles = BTM_WAIT_LIMIT_CYCLES)
 {
     if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
         if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > BTM_WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
             atomicCAS(status, 0, code);
             return false;
@@ -150,10 +151,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // Warp-collective form for the epilogue warps: one lane waits, the outcome is broadcast, so 31 lanes
 // per warp do not poll. All 32 lanes must call it.
 template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                               long long limit_cycles = BTM_WAIT_LIMIT_CYCLES)
 {
     int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait<kCluster>(bar, parity, abort_flag, status, code) ? 1 : 0;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait<kCluster>(bar, parity, abort_flag, status, code, limit_cycles) ? 1 : 0;
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 

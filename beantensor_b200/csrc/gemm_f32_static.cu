@@ -39,13 +39,8 @@ constexpr int kMaxDevices = 64;
 StaticDeviceState g_state[kMaxDevices];
 std::mutex g_mu;
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn g_encode_fn = nullptr;
-
 // One-time set-up for `device`, which the caller has already made current. No allocation:
-// symbol lookups, a driver entry-point lookup and kernel attribute changes only.
+// symbol lookups and kernel attribute changes only.
 StaticDeviceState *setup(int device, int *code)
 {
     std::lock_guard<std::mutex> lock(g_mu);
@@ -62,37 +57,12 @@ StaticDeviceState *setup(int device, int *code)
     void *scratch = nullptr, *status = nullptr;
     if (btm::check_cuda(cudaGetSymbolAddress(&scratch, g_static_scratch), "cudaGetSymbolAddress(static scratch)")) return nullptr;
     if (btm::check_cuda(cudaGetSymbolAddress(&status, g_static_status), "cudaGetSymbolAddress(static status)")) return nullptr;
-    if (!g_encode_fn) {
-        void *fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (btm::check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint"))
-            return nullptr;
-        if (qres != cudaDriverEntryPointSuccess || !fn) {
-            btm::set_error(BTM_ERR_CUDA, "CUDA Error: driver does not export cuTensorMapEncodeTiled");
-            return nullptr;
-        }
-        g_encode_fn = (EncodeTiledFn)fn;
-    }
     if (btm::configure_gemm_tc_kernels()) return nullptr;
     s->scratch = scratch;
     s->status = (int *)status;
     s->sm_count = prop.multiProcessorCount;
     s->ready = true;
     return s;
-}
-
-int encode_f32_planes(CUtensorMap *out, const void *base, uint64_t k, uint64_t rows, uint64_t pitch_bytes, uint64_t plane_bytes,
-                      uint32_t box_rows)
-{
-    cuuint64_t dims[3] = {k, rows, 2};
-    cuuint64_t strides[2] = {pitch_bytes, plane_bytes};
-    cuuint32_t box[3] = {32, box_rows, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode_fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(base), dims, strides, box, estr,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return btm::set_error(BTM_ERR_CUDA, "CUDA Error: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    return BTM_OK;
 }
 
 } // namespace
@@ -129,18 +99,30 @@ extern "C" int btm_gemm_f32_static(int device, void *stream, int M, int N, int K
     if (!s) return setup_code;
     cudaStream_t st = (cudaStream_t)stream;
 
-    // A wait that ran out in an earlier call of this entry point left a code in the private status
-    // word. Look at it only when the stream is idle, so that the check never stalls queued work.
-    if (cudaStreamQuery(st) == cudaSuccess) {
-        int code = 0;
-        rc = check_cuda(cudaMemcpy(&code, s->status, sizeof(int), cudaMemcpyDeviceToHost), "status readback");
-        if (rc) return rc;
-        if (code != 0) {
-            cudaMemset(s->status, 0, sizeof(int));
-            return set_error(BTM_ERR_TIMEOUT, "CUDA Error: a kernel wait ran out in an earlier call (device status %d)", code);
+    // A wait that ran out in an earlier call of this entry point left a code in the private status word. It is
+    // looked at only when `stream` is not being captured and has nothing queued: the read then goes through
+    // `stream` itself (no other stream is touched) and returns at once.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    rc = check_cuda(cudaStreamIsCapturing(st, &cap), "cudaStreamIsCapturing");
+    if (rc) return rc;
+    if (cap == cudaStreamCaptureStatusNone) {
+        const cudaError_t q = cudaStreamQuery(st);
+        if (q == cudaSuccess) {
+            int code = 0;
+            rc = check_cuda(cudaMemcpyAsync(&code, s->status, sizeof(int), cudaMemcpyDeviceToHost, st), "status readback");
+            if (rc) return rc;
+            rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+            if (rc) return rc;
+            if (code != 0) {
+                rc = check_cuda(cudaMemsetAsync(s->status, 0, sizeof(int), st), "status clear");
+                if (rc) return rc;
+                return set_error(BTM_ERR_TIMEOUT, "CUDA Error: a kernel wait ran out in an earlier call (device status %d)", code);
+            }
+        } else if (q == cudaErrorNotReady) {
+            (void)cudaGetLastError(); // work is queued: expected, and it must not stick as the thread's last error
+        } else {
+            return check_cuda(q, "cudaStreamQuery");
         }
-    } else {
-        (void)cudaGetLastError(); // cudaErrorNotReady is expected here and must not stick
     }
 
     if (K == 0) return launch_gemm_simt(BTM_F32, st, 1, M, N, 0, A, lda, 0, B, ldb, 0, C, ldc, 0);
@@ -155,9 +137,9 @@ extern "C" int btm_gemm_f32_static(int device, void *stream, int M, int N, int K
     const long long t128 = (long long)((M + 127) / 128) * ((N + 127) / 128);
     const int bn = t128 < s->sm_count ? 64 : 128;
     CUtensorMap tmA, tmB;
-    rc = encode_f32_planes(&tmA, a_hi, (uint64_t)K, (uint64_t)M, (uint64_t)Kp * 4, (uint64_t)a_plane * 4, 128);
+    rc = encode_tmap_3d(&tmA, BTM_F32, a_hi, (uint64_t)K, (uint64_t)M, 2, (uint64_t)Kp * 4, (uint64_t)a_plane * 4, 32, 128);
     if (rc) return rc;
-    rc = encode_f32_planes(&tmB, b_hi, (uint64_t)K, (uint64_t)N, (uint64_t)Kp * 4, (uint64_t)b_plane * 4, (uint32_t)bn);
+    rc = encode_tmap_3d(&tmB, BTM_F32, b_hi, (uint64_t)K, (uint64_t)N, 2, (uint64_t)Kp * 4, (uint64_t)b_plane * 4, 32, (uint32_t)bn);
     if (rc) return rc;
     GemmParams p;
     memset(&p, 0, sizeof(p));
@@ -169,9 +151,11 @@ extern "C" int btm_gemm_f32_static(int device, void *stream, int M, int N, int K
     p.ndst = 1;
     p.C[0] = C;
     p.ldc = ldc;
-    p.c_vec_ok = 0; // per-thread row stores: this variant encodes no output tensor map
+    p.c_vec_ok = ((((uintptr_t)C) & 15) == 0 && (ldc * 4) % 16 == 0) ? 1 : 0; // same store path as btm_gemm
     p.status = s->status;
+    fill_wait_params(&p);
     StoreMaps cm;
-    memset(&cm, 0, sizeof(cm));
+    rc = encode_store_maps(&cm, BTM_F32, p);
+    if (rc) return rc;
     return launch_gemm_tc(BTM_F32, st, s->sm_count, tmA, tmB, cm, p, bn);
 }

@@ -126,14 +126,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (lane == 0 && !p.debug_skip_loads) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const TileCoord tc = decode_tile<BN>(p, tile);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
+                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY, p.wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -177,11 +177,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t idesc = tile < p.tiles_full ? idesc_full : idesc_half;
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag, p.status, WAIT_MMA_TMEM_EMPTY)) break;
+                if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag, p.status, WAIT_MMA_TMEM_EMPTY, p.wait_limit)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.status, WAIT_MMA_FULL)) {
+                    if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.status, WAIT_MMA_FULL, p.wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -228,7 +228,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int acc = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             // One lane waits and broadcasts the outcome: tcgen05.ld below needs the whole warp.
-            if (!mbar_wait_warp(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL)) break;
+            if (!mbar_wait_warp(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL, p.wait_limit)) break;
             tc_fence_after();
             epilogue_band<DT>(p, cmaps, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN), tc.m * BM + quad * 32, tc.n0,
                               tc.bn, tc.b, epi_smem, epi_tiles, lane);
@@ -256,6 +256,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
 }
 
+// Low part of the split. For an infinite x the high part is already x and x - hi would be Inf - Inf = NaN, which
+// would turn a whole output row or column into NaN where an fp32 product gives +-Inf; the low part is 0 there.
+__device__ __forceinline__ float split_lo(float x, float hi) { return fabsf(x) == INFINITY ? 0.0f : x - hi; }
+
 // 3xTF32 operand preparation: hi = x with the low 13 mantissa bits cleared (what the tensor
 // core reads of an fp32 word), lo = x - hi (exact in fp32). Written as two dense planes.
 __global__ void split_tf32_kernel(const float *__restrict__ src, long long ld, int rows, int cols,
@@ -268,7 +272,7 @@ __global__ void split_tf32_kernel(const float *__restrict__ src, long long ld, i
         float x = (c < cols) ? src[r * ld + c] : 0.0f;
         const float h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
         hi[i] = h;
-        lo[i] = x - h;
+        lo[i] = split_lo(x, h);
     }
 }
 
@@ -290,7 +294,7 @@ __global__ void split_tf32_transpose_kernel(const float *__restrict__ src, long 
             const float x = tile[threadIdx.x][i];
             const float h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
             hi[(long long)c * ld_dst + r] = h;
-            lo[(long long)c * ld_dst + r] = x - h;
+            lo[(long long)c * ld_dst + r] = split_lo(x, h);
         }
     }
 }
@@ -311,7 +315,7 @@ __global__ void split_tf32_pair_kernel(const float *__restrict__ A, long long ld
                 const float x = c < K ? A[(long long)r * lda + c] : 0.0f;
                 const float h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
                 a_hi[(long long)r * Kp + c] = h;
-                a_lo[(long long)r * Kp + c] = x - h;
+                a_lo[(long long)r * Kp + c] = split_lo(x, h);
             }
         }
         return;
@@ -329,7 +333,7 @@ __global__ void split_tf32_pair_kernel(const float *__restrict__ A, long long ld
             const float x = tile[threadIdx.x][i];
             const float h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
             b_hi[(long long)c * Kp + r] = h;
-            b_lo[(long long)c * Kp + r] = x - h;
+            b_lo[(long long)c * Kp + r] = split_lo(x, h);
         }
     }
 }

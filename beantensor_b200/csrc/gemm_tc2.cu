@@ -136,7 +136,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (both CTAs)
-        if (lane == 0) {
+        if (lane == 0 && !p.debug_skip_loads) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -146,7 +146,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int chunks = half_bn >> 6;     // 64-column chunks: 2 or 1
                 const uint32_t cta_bytes = (uint32_t)(A_BYTES + chunks * CHUNK_BYTES);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!mbar_wait<true>(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
+                    if (!mbar_wait<true>(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY, p.wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -180,11 +180,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const uint32_t idesc = pt.bn == BN ? idesc_full : idesc_half;
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait<true>(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag, p.status, WAIT_MMA_TMEM_EMPTY)) break;
+                if (!mbar_wait<true>(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag, p.status, WAIT_MMA_TMEM_EMPTY, p.wait_limit)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!mbar_wait<true>(smem_u32(&bar_full[stage]), phase, &abort_flag, p.status, WAIT_MMA_FULL)) {
+                    if (!mbar_wait<true>(smem_u32(&bar_full[stage]), phase, &abort_flag, p.status, WAIT_MMA_FULL, p.wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -216,7 +216,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int acc = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             // One lane waits and broadcasts the outcome: tcgen05.ld below needs the whole warp.
-            if (!mbar_wait_warp<true>(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL)) break;
+            if (!mbar_wait_warp<true>(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag, p.status, WAIT_EPI_TMEM_FULL, p.wait_limit)) break;
             tc_fence_after();
             epilogue_band<DT>(p, cmaps, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN),
                               pt.m * PAIR_M + (int)rank * CTA_M + quad * 32, pt.n0, pt.bn, pt.b, epi_smem, epi_tiles, lane);

@@ -763,7 +763,9 @@ int configure_int4_gemv_kernels()
 {
     cudaError_t e = cudaFuncSetAttribute(int4_gemv_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 150 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(int4_gemv_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 150 * 1024);
-    return check_cuda(e, "cudaFuncSetAttribute(int4_gemv_stream)");
+    int rc = check_cuda(e, "cudaFuncSetAttribute(int4_gemv_stream)");
+    if (rc) return rc;
+    return configure_int4_gemv_rows_kernels();
 }
 
 int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
@@ -805,6 +807,13 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
         if (rc) return rc;
         return check_cuda(cudaGetLastError(), "int4 gemm launch");
     }
+    // M <= 8: the register-resident kernel (int4_gemv_rows.cu) unless the caller pins one of the two kernels below
+    // (BTM_FORCE_GEMV=stream|slab; rows8 selects its twenty-warp form). Shapes it does not take fall through.
+    const char *force_gemv = getenv("BTM_FORCE_GEMV");
+    if (!(force_gemv && (!strcmp(force_gemv, "stream") || !strcmp(force_gemv, "slab")))) {
+        const int rc_rows = launch_int4_gemv_rows(st, sm_count, M, N, K, group, act, w, scales, out, (force_gemv && !strcmp(force_gemv, "rows8")) ? 8 : 16);
+        if (rc_rows != -1) return rc_rows;
+    }
     const bool stage_act = M <= 2; // slab kernel: a slab and more than two staged rows do not fit together
     const int npieces = (K / 128 + 1) / 2;
     // Streaming kernel: K long enough to give each of its eight warps a 128-k block, a block's scales a whole
@@ -813,7 +822,6 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
     // (the next launch then fits on the SM beside this one), up to 150 KB for more rows (13.1 -> 10.9 us at M = 8:
     // the permuted copy takes four global loads and eight byte-permutes per 128-k block out of the inner loop,
     // which is worth more there than the early residency of the successor).
-    const char *force_gemv = getenv("BTM_FORCE_GEMV");
     const int mrows_s = M < 8 ? M : 8;
     const size_t smem_base_s = (size_t)GS_STAGES * GEMV_ROWS * (K / 2 + ((192 - ((K / 2) & 127)) & 127) + (K / group) * 2) +
                                (((size_t)GS_RED * GS_WARPS * 16 * mrows_s * 4 + 15) & ~(size_t)15);

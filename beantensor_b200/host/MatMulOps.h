@@ -5,7 +5,7 @@
 //
 // The functions take btm_tensor_view, a POD mirror of the Tensor fields the path reads
 // (Tensor/Tensor.h:173-201). Inside the reference tree a maintainer fills it from a Tensor in a
-// friend function (see INTEGRATION.md) and defines BT_HAVE_REFERENCE_ERRORS so that the
+// friend function and defines BT_HAVE_REFERENCE_ERRORS so that the
 // exception types come from Errors/Logic.h instead of the stand-ins below.
 #pragma once
 #include <cstdint>

@@ -22,7 +22,8 @@
  *     Tensor::data, cf. Tensor/TensorOps.cu:89-208);
  *   - the return value is a btm_status; a C ABI cannot throw, so the C++ binding maps the
  *     status back to the reference's exception types (Errors/Logic.h:13-38);
- *   - calls are re-entrant and may come from any thread (Helper/Threads/CPUThreading.h:37-56).
+ *   - calls are re-entrant and may come from any thread (Helper/Threads/CPUThreading.h:37-56); two calls share
+ *     nothing but read-only per-device state, unless an entry point below says otherwise.
  * There is no CPU fallback: without a usable sm_100 device every compute call fails with
  * BTM_ERR_CUDA or BTM_ERR_UNSUPPORTED.
  */
@@ -93,6 +94,13 @@ int btm_version(void);
  * the what() string of the exceptions the reference throws (Errors/Logic.h:13-59). */
 const char *btm_last_error_string(void);
 
+/* Test hooks, no counterpart in the reference. Process-wide switches that make the bounded waits inside the
+ * matmul kernels observable without any fault: "wait_limit_cycles" (SM cycles after which a kernel wait gives
+ * up; 0 restores the default of about one second) and "skip_loads" (non-zero: the producer warps of the dense
+ * matmul kernels issue no loads, so the consumers' waits run out, the kernel unwinds, returns, and the next
+ * btm_check_device_status reports BTM_ERR_TIMEOUT). Unknown keys return BTM_ERR_INVALID. */
+int btm_debug_set(const char *key, long long value);
+
 /* Prepare `device`: checks that it is an sm_100 part, creates the per-device state
  * (status word, kernel attributes). Every compute call does this lazily; call it up front
  * to keep the first timed call clean. Stands where the reference's workers do their
@@ -109,8 +117,11 @@ int btm_check_device_status(int device, void *stream);
  *   dtype BTM_F16 / BTM_BF16: fp32 accumulation on the tensor cores, output rounded to
  *   nearest even into the same 16-bit type (as Tensor/TensorOps.cu:72 rounds).
  *   dtype BTM_F32: three-term TF32 split (hi.hi + hi.lo + lo.hi) with fp32 accumulation;
- *   needs (M + N) * roundup(K,4) * 8 bytes of scratch that the library keeps per device and grows
- *   with cudaMalloc on demand (first call of a larger shape allocates).
+ *   needs (M + N) * roundup(K,4) * 8 bytes of scratch. Every call takes its own block from a memory
+ *   pool that the library keeps per device and returns it in stream order on `stream`
+ *   (cudaMallocFromPoolAsync / cudaFreeAsync), so concurrent calls on other streams or threads never
+ *   share scratch; freed blocks stay in the pool, and only the first call of a larger shape reaches
+ *   the driver. Infinite inputs give infinite (not NaN) outputs, as a plain fp32 product would.
  * lda >= K, ldb >= N, ldc >= N, in elements. Any M, N, K >= 0; shapes or pointers that
  * the tensor-core path cannot address (row pitch or base not 16-byte aligned) run on a
  * general CUDA-core kernel with the same arithmetic contract. */
@@ -157,7 +168,8 @@ int btm_gemm_f32_ws(int device, void *stream, int M, int N, int K, const void *A
  *   - the first call on a device looks up the array's device address (once per device); make that
  *     first call before starting any stream capture.
  *   - a kernel wait that ran out is reported by a later call of this function on the same device
- *     (BTM_ERR_TIMEOUT), checked only when `stream` is idle. */
+ *     (BTM_ERR_TIMEOUT). That check reads one word back through `stream` and is made only when
+ *     `stream` is idle and not being captured; no other stream is touched. */
 #define BTM_STATIC_SCRATCH_BYTES (64ull << 20)
 int btm_gemm_f32_static(int device, void *stream, int M, int N, int K, const void *A, int64_t lda, const void *B,
                         int64_t ldb, void *C, int64_t ldc);
@@ -214,6 +226,14 @@ int btm_int4_unpack(int device, void *stream, int N, int K, const void *w_packed
  * the cross-rank barrier before C is read. dtype BTM_F16 or BTM_BF16. */
 int btm_gemm_nshard(int device, void *stream, int dtype, int M, int Nloc, int K, const void *A, int64_t lda,
                     const void *B_local, int64_t ldb, void *const *C_ranks, int64_t ldc, int rank, int nranks);
+
+/* Placement helper for an operand that every rank needs whole (A of the N-sharded product) when each rank has
+ * only a slice of it at hand: `bufs[r]` is rank r's copy of the operand (peer-mapped, as for btm_gemm_nshard), and the
+ * byte range [offset_bytes, offset_bytes + bytes) of this rank's copy is sent to the same range of every other
+ * rank's copy with one asynchronous copy per peer on `stream`. When all ranks have done this for their own ranges
+ * and a cross-rank barrier has passed, every copy is complete: an all-gather by placement. Extends the reference's
+ * move_gpu_to_gpu (Tensor/TensorOps.cu:282-313), which copies one whole tensor to one other GPU. */
+int btm_replicate_rows(int device, void *stream, void *const *bufs, int rank, int nranks, size_t offset_bytes, size_t bytes);
 
 /* CUDA IPC helpers so that one-process-per-GPU callers can build `C_ranks`:
  * btm_ipc_alloc allocates `bytes` of device memory and writes a 64-byte handle;

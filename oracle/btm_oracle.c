@@ -20,6 +20,7 @@
  *
  * Plain C11, no dependencies beyond libm and pthreads.
  */
+#define _POSIX_C_SOURCE 200809L
 #include <math.h>
 #include <pthread.h>
 #include <stdint.h>
@@ -418,18 +419,29 @@ void btmo_ref_random_f64(double *out, size_t numel, uint64_t seed, double lo, do
 }
 
 /* ------------------------------------------------------------------------------------
- * Timed CPU baseline ("port"): binary32 blocked matmul over host threads. The reference
- * has no CPU matmul to time (its AVX-512 code converts dtypes only,
- * Intrinsics/AVX512/DTypeConversions.cpp:10-174), so this stands in for it; rows are
- * split over threads as the reference splits CPU work (Tensor/Tensor.cpp:141-151).
- * Inputs are widened to binary32 by the caller outside the timed region.
+ * Timed CPU baseline ("port"): binary32 matmul over host threads. The reference has no
+ * CPU matmul to time (its AVX-512 code converts dtypes only,
+ * Intrinsics/AVX512/DTypeConversions.cpp:10-174), so this stands in for it, written the
+ * way a tuned CPU GEMM is: B is packed per k-block into panels of 32 columns, a
+ * register-blocked 12 x 32 micro-kernel (24 accumulator vectors, AVX-512 FMA) runs over
+ * it, and rows are split over threads as the reference splits CPU work
+ * (Tensor/Tensor.cpp:141-151). Hosts without AVX-512, and the ragged edges, take the plain
+ * loop. Inputs are widened to binary32 by the caller outside the timed region.
  * ---------------------------------------------------------------------------------- */
+
+#define FAST_MR 12
+#define FAST_NR 32
+#define FAST_KC 384
 
 typedef struct {
     int64_t M, N, K;
     const float *A, *B;
     float *C;
+    float *Bp;            /* packed k-block of B: [N / 32 panels][kc][32] */
+    int tid, threads;
     int64_t row0, row1;
+    int use_avx512;
+    pthread_barrier_t *bar;
 } fast_job;
 
 #if defined(__x86_64__) && defined(__GNUC__)
@@ -448,35 +460,116 @@ static void fast_block(const float *A, const float *B, float *C, int64_t N, int6
     }
 }
 
+#if defined(__x86_64__) && defined(__GNUC__)
+#include <immintrin.h>
+/* C[12 x 32] += Ap[kc x 12] . Bp[kc x 32]; both operands packed (Ap: 12 row values per k, Bp: 32 columns per k). */
+__attribute__((target("avx512f")))
+static void fast_micro_12x32(const float *Ap, const float *Bp, float *C, int64_t ldc, int64_t kc)
+{
+    __m512 c0[FAST_MR], c1[FAST_MR];
+#pragma GCC unroll 12
+    for (int i = 0; i < FAST_MR; ++i) {
+        c0[i] = _mm512_loadu_ps(C + i * ldc);
+        c1[i] = _mm512_loadu_ps(C + i * ldc + 16);
+    }
+    for (int64_t k = 0; k < kc; ++k) {
+        const __m512 b0 = _mm512_loadu_ps(Bp + k * FAST_NR), b1 = _mm512_loadu_ps(Bp + k * FAST_NR + 16);
+#pragma GCC unroll 12
+        for (int i = 0; i < FAST_MR; ++i) {
+            const __m512 a = _mm512_set1_ps(Ap[k * FAST_MR + i]);
+            c0[i] = _mm512_fmadd_ps(a, b0, c0[i]);
+            c1[i] = _mm512_fmadd_ps(a, b1, c1[i]);
+        }
+    }
+#pragma GCC unroll 12
+    for (int i = 0; i < FAST_MR; ++i) {
+        _mm512_storeu_ps(C + i * ldc, c0[i]);
+        _mm512_storeu_ps(C + i * ldc + 16, c1[i]);
+    }
+}
+static int host_has_avx512(void) { return __builtin_cpu_supports("avx512f"); }
+#else
+static void fast_micro_12x32(const float *Ap, const float *Bp, float *C, int64_t ldc, int64_t kc)
+{
+    (void)Ap; (void)Bp; (void)C; (void)ldc; (void)kc;
+}
+static int host_has_avx512(void) { return 0; }
+#endif
+
 static void *fast_worker(void *arg)
 {
     fast_job *j = (fast_job *)arg;
-    const int64_t BK = 256, BN = 1024;
-    for (int64_t i = j->row0; i < j->row1; ++i) memset(j->C + i * j->N, 0, sizeof(float) * (size_t)j->N);
-    for (int64_t n0 = 0; n0 < j->N; n0 += BN)
-        for (int64_t k0 = 0; k0 < j->K; k0 += BK) {
-            int64_t n1 = n0 + BN < j->N ? n0 + BN : j->N;
-            int64_t k1 = k0 + BK < j->K ? k0 + BK : j->K;
-            fast_block(j->A, j->B, j->C, j->N, j->K, j->row0, j->row1, k0, k1, n0, n1);
+    const int64_t N = j->N, K = j->K;
+    const int64_t panels = N / FAST_NR;            /* full 32-column panels; the rest takes the plain loop */
+    for (int64_t i = j->row0; i < j->row1; ++i) memset(j->C + i * N, 0, sizeof(float) * (size_t)N);
+    if (!j->use_avx512) {
+        const int64_t BK = 256, BN = 1024;
+        for (int64_t n0 = 0; n0 < N; n0 += BN)
+            for (int64_t k0 = 0; k0 < K; k0 += BK)
+                fast_block(j->A, j->B, j->C, N, K, j->row0, j->row1, k0, k0 + BK < K ? k0 + BK : K, n0, n0 + BN < N ? n0 + BN : N);
+        return NULL;
+    }
+    const int64_t rows_main = j->row0 + (j->row1 - j->row0) / FAST_MR * FAST_MR;
+    /* this thread's rows of A, packed per k-block: [row block of 12][k][12] */
+    float *Ap = NULL;
+    if (rows_main > j->row0 && posix_memalign((void **)&Ap, 64, sizeof(float) * (size_t)(rows_main - j->row0) * FAST_KC)) Ap = NULL;
+    for (int64_t k0 = 0; k0 < K; k0 += FAST_KC) {
+        const int64_t kc = k0 + FAST_KC < K ? FAST_KC : K - k0;
+        if (Ap)
+            for (int64_t i = j->row0; i < rows_main; i += FAST_MR) {
+                float *dst = Ap + (i - j->row0) * FAST_KC;
+                for (int r = 0; r < FAST_MR; ++r) {
+                    const float *src = j->A + (i + r) * K + k0;
+                    for (int64_t k = 0; k < kc; ++k) dst[k * FAST_MR + r] = src[k];
+                }
+            }
+        /* every thread packs its share of the panels of this k-block */
+        for (int64_t p = j->tid; p < panels; p += j->threads) {
+            float *dst = j->Bp + p * FAST_KC * FAST_NR;
+            const float *src = j->B + k0 * N + p * FAST_NR;
+            for (int64_t k = 0; k < kc; ++k) memcpy(dst + k * FAST_NR, src + k * N, sizeof(float) * FAST_NR);
         }
+        pthread_barrier_wait(j->bar);
+        for (int64_t p = 0; p < panels; ++p) {
+            const float *bp = j->Bp + p * FAST_KC * FAST_NR;
+            if (Ap)
+                for (int64_t i = j->row0; i < rows_main; i += FAST_MR)
+                    fast_micro_12x32(Ap + (i - j->row0) * FAST_KC, bp, j->C + i * N + p * FAST_NR, N, kc);
+        }
+        if (!Ap && rows_main > j->row0) fast_block(j->A, j->B, j->C, N, K, j->row0, rows_main, k0, k0 + kc, 0, panels * FAST_NR);
+        if (rows_main < j->row1) fast_block(j->A, j->B, j->C, N, K, rows_main, j->row1, k0, k0 + kc, 0, panels * FAST_NR);
+        if (panels * FAST_NR < N) fast_block(j->A, j->B, j->C, N, K, j->row0, j->row1, k0, k0 + kc, panels * FAST_NR, N);
+        pthread_barrier_wait(j->bar); /* the packed block is rewritten next round */
+    }
+    free(Ap);
     return NULL;
 }
 
 int btmo_gemm_f32_threads(int64_t M, int64_t N, int64_t K, const float *A, const float *B, float *C, int threads)
 {
-    threads = clamp_threads(threads, M);
+    if (M <= 0 || N <= 0) return 0;
+    threads = clamp_threads(threads, (M + FAST_MR - 1) / FAST_MR);
+    /* rows per thread: a multiple of the micro-kernel's 12 where possible */
+    int64_t chunk = (M + threads - 1) / threads;
+    chunk = (chunk + FAST_MR - 1) / FAST_MR * FAST_MR;
+    int used = (int)((M + chunk - 1) / chunk);
     fast_job jobs[256];
     pthread_t tids[256];
-    int64_t chunk = (M + threads - 1) / threads;
-    int started = 0;
-    for (int t = 0; t < threads; ++t) {
-        int64_t r0 = t * chunk, r1 = r0 + chunk < M ? r0 + chunk : M;
-        if (r0 >= M) break;
-        jobs[t] = (fast_job){M, N, K, A, B, C, r0, r1};
-        pthread_create(&tids[t], NULL, fast_worker, &jobs[t]);
-        ++started;
+    pthread_barrier_t bar;
+    const int avx = host_has_avx512();
+    float *Bp = NULL;
+    if (avx) {
+        if (posix_memalign((void **)&Bp, 64, sizeof(float) * (size_t)FAST_KC * (size_t)(N / FAST_NR + 1) * FAST_NR)) return 1;
     }
-    for (int t = 0; t < started; ++t) pthread_join(tids[t], NULL);
+    pthread_barrier_init(&bar, NULL, (unsigned)used);
+    for (int t = 0; t < used; ++t) {
+        int64_t r0 = t * chunk, r1 = r0 + chunk < M ? r0 + chunk : M;
+        jobs[t] = (fast_job){M, N, K, A, B, C, Bp, t, used, r0, r1, avx, &bar};
+        pthread_create(&tids[t], NULL, fast_worker, &jobs[t]);
+    }
+    for (int t = 0; t < used; ++t) pthread_join(tids[t], NULL);
+    pthread_barrier_destroy(&bar);
+    free(Bp);
     return 0;
 }
 

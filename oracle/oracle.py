@@ -29,12 +29,16 @@ def build(force: bool = False) -> str:
     return _SO
 
 
-def build_ref(ref_root: str = "/root/reference") -> str | None:
-    """Compile the reference's own Tensor::random driver when its sources are present."""
+def build_ref(ref_root: str | None = None) -> str | None:
+    """Compile the reference's own Tensor::random driver when its sources are present. The reference tree is
+    `ref_root`, else the environment variable BTM_REFERENCE_ROOT, else a directory named `reference` beside this
+    repository; without any of them only an already built driver is returned."""
     out = os.path.join(_HERE, "_ref", "ref_random")
     if os.path.exists(out):
         return out
-    if not os.path.isdir(ref_root):
+    sibling = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    ref_root = ref_root or os.environ.get("BTM_REFERENCE_ROOT") or sibling
+    if not os.path.isfile(os.path.join(ref_root, "Tensor", "Tensor.cpp")):
         return None
     subprocess.check_call(["make", "-C", _HERE, "ref", f"REF={ref_root}"], stdout=subprocess.DEVNULL)
     return out

@@ -206,3 +206,112 @@ def test_concurrent_callers_on_their_own_streams(btm, oracle):
     for i in range(4):
         got, A, B = results[i]
         assert oracle.rel_frobenius(got, dtype, oracle.gemm(dtype, A, B)) <= TOL[dtype], shapes[i]
+
+
+def test_concurrent_fp32_callers_with_growing_shapes(btm, oracle):
+    # fp32 products need scratch. Each call gets its own block in stream order, so four host threads on four
+    # streams with different shapes (a small one first, larger ones after it, so that later calls need more
+    # scratch than earlier ones were given) must not disturb one another.
+    import threading
+    import torch
+    dtype = _lib.F32
+    shapes = [[(64, 64, 64), (512, 384, 256), (1024, 1024, 512)], [(128, 256, 128), (1000, 1000, 992), (256, 256, 256)],
+              [(96, 160, 40), (768, 512, 1024), (1536, 512, 256)], [(257, 129, 65), (384, 2048, 512), (640, 640, 640)]]
+    results, errors = {}, []
+
+    def worker(i):
+        try:
+            stream = torch.cuda.Stream()
+            got = []
+            with torch.cuda.stream(stream):
+                for rep in range(3):
+                    for (M, N, K) in shapes[i]:
+                        A, B = gemm_inputs(dtype, M, N, K, 90 + i, "uniform")
+                        a, b = to_gpu(A, dtype), to_gpu(B, dtype)
+                        out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+                        btm.matmul_gpu(a, b, out)
+                        if rep == 2:
+                            got.append((out, A, B))
+                stream.synchronize()
+            results[i] = [(to_host_bits(o, dtype), A, B) for (o, A, B) in got]
+        except Exception as e:  # surfaced below, in the main thread
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    btm.check_device_status(0)
+    for i in range(4):
+        for (got, A, B), shape in zip(results[i], shapes[i]):
+            assert oracle.rel_frobenius(got, dtype, oracle.gemm(dtype, A, B)) <= TOL[dtype], shape
+
+
+def test_fp32_non_finite_inputs(btm):
+    # One infinite element makes its output row / column infinite, not NaN (the low half of the split of an
+    # infinity is 0, not Inf - Inf); a NaN input still poisons what it touches and nothing else.
+    import torch
+    M = N = K = 128
+    a = torch.rand((M, K), dtype=torch.float32, device="cuda") + 0.5
+    b = torch.rand((K, N), dtype=torch.float32, device="cuda") + 0.5
+    a[3, 5] = float("inf")
+    b[7, 9] = float("-inf")
+    a[100, 1] = float("nan")
+    out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    btm.matmul_gpu(a, b, out)
+    btm.check_device_status(0)
+    ref = a.double() @ b.double()
+    assert torch.equal(torch.isnan(out), torch.isnan(ref))
+    assert torch.equal(torch.isposinf(out), torch.isposinf(ref))
+    assert torch.equal(torch.isneginf(out), torch.isneginf(ref))
+    fin = torch.isfinite(ref)
+    assert ((out.double() - ref)[fin].norm() / ref[fin].norm()).item() <= 1e-5
+
+
+def test_fp32_with_caller_owned_scratch(btm, oracle):
+    import ctypes as C
+    import torch
+    L = _lib.lib()
+    M, N, K = 300, 200, 130
+    A, B = gemm_inputs(_lib.F32, M, N, K, 5, "uniform")
+    a, b = to_gpu(A, _lib.F32), to_gpu(B, _lib.F32)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    need = L.btm_gemm_f32_workspace_bytes(M, N, K)
+    assert need == (M + N) * 132 * 8
+    ws = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
+    base = (ws.data_ptr() + 255) & ~255
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert L.btm_gemm_f32_ws(0, st, M, N, K, a.data_ptr(), K, b.data_ptr(), N, out.data_ptr(), N, base, need) == _lib.OK, _lib.last_error()
+    btm.check_device_status(0)
+    assert oracle.rel_frobenius(to_host_bits(out, _lib.F32), _lib.F32, oracle.gemm(_lib.F32, A, B)) <= 1e-5
+    # too small or misaligned scratch is refused
+    assert L.btm_gemm_f32_ws(0, st, M, N, K, a.data_ptr(), K, b.data_ptr(), N, out.data_ptr(), N, base, need - 1) == _lib.ERR_INVALID
+    assert L.btm_gemm_f32_ws(0, st, M, N, K, a.data_ptr(), K, b.data_ptr(), N, out.data_ptr(), N, base + 8, need) == _lib.ERR_INVALID
+
+
+@pytest.mark.parametrize("dtype", [_lib.F16, _lib.F32])
+def test_user_level_matmul_and_views_with_an_offset(btm, oracle, dtype):
+    # ops.matmul allocates the result and dispatches by rank (the Ops::add sketch's style); operands that are
+    # views into a larger allocation (offset != 0, row pitch larger than the row) go through unchanged.
+    import torch
+    M, N, K = 200, 264, 136
+    A, B = gemm_inputs(dtype, M, N, K, 41, "uniform" if dtype == _lib.F32 else "normal")
+    big_a = torch.zeros((M + 3, K + 24), dtype=torch_dtype(dtype), device="cuda")
+    big_b = torch.zeros((K + 2, N + 8), dtype=torch_dtype(dtype), device="cuda")
+    big_a[3:, 16:16 + K] = to_gpu(A, dtype)
+    big_b[2:, 8:8 + N] = to_gpu(B, dtype)
+    a, b = big_a[3:, 16:16 + K], big_b[2:, 8:8 + N]
+    assert a.storage_offset() != 0 and b.storage_offset() != 0
+    out = btm.matmul(a, b)
+    btm.check_device_status(0)
+    assert out.shape == (M, N) and out.dtype == torch_dtype(dtype)
+    ref = oracle.gemm(dtype, A, B)
+    assert oracle.rel_frobenius(to_host_bits(out, dtype), dtype, ref) <= TOL[dtype]
+    if dtype == _lib.F16:
+        A3 = np.stack([A, A[::-1].copy()])
+        B3 = np.stack([B, B[:, ::-1].copy()])
+        out3 = btm.matmul(to_gpu(A3, dtype), to_gpu(B3, dtype))
+        assert out3.shape == (2, M, N)
+        assert oracle.rel_frobenius(to_host_bits(out3, dtype), dtype, oracle.bmm(dtype, A3, B3)) <= TOL[dtype]

@@ -98,14 +98,15 @@ def test_bad_arguments(btm):
                             torch.zeros((1, 16), dtype=torch.float16, device="cuda"), 128)
 
 
-@pytest.mark.parametrize("path", ["stream", "slab"])
+@pytest.mark.parametrize("path", ["rows", "rows8", "stream", "slab"])
 @pytest.mark.parametrize("case", [(1, 11008, 4096, 128), (8, 11008, 4096, 128), (3, 100, 4096, 128), (2, 37, 2048, 128),
-                                  (1, 48, 2304, 128), (5, 16, 8192, 256), (2, 3000, 4096, 128)])
+                                  (1, 48, 2304, 128), (5, 16, 8192, 256), (2, 3000, 4096, 128), (4, 5000, 1024, 128), (7, 129, 11008, 128),
+                                  (8, 40, 12288, 512), (6, 2049, 640, 128)])
 def test_gemv_both_kernels(btm, oracle, case, path, monkeypatch):
-    # M <= 8: the persistent streaming kernel, or (pinned) the kernel that stages one whole 16-row slab per CTA.
+    # M <= 8: the register-resident kernel (ten or twenty warps per CTA), or pinned to the persistent streaming
+    # kernel or to the kernel that stages one whole 16-row slab per CTA.
     M, N, K, group = case
-    if path == "slab":
-        monkeypatch.setenv("BTM_FORCE_GEMV", "slab")
+    monkeypatch.setenv("BTM_FORCE_GEMV", path)
     w, packed, s, act = make(M, N, K, group, 23 + M + N)
     out = gpu_matmul(btm, act, packed, s, group)
     assert not np.isnan(out).any()
@@ -118,7 +119,7 @@ def test_gemv_both_kernels(btm, oracle, case, path, monkeypatch):
 @pytest.mark.parametrize("case", [(16, 128, 256, 128), (64, 1088, 1024, 128), (100, 200, 512, 64), (129, 72, 1024, 256), (40, 64, 4096, 128),
                                   (16, 19200, 256, 128), (24, 12800, 512, 128), (20, 33, 384, 128)])
 def test_more_than_eight_rows_both_paths(btm, oracle, case, path, monkeypatch):
-    # M > 8 runs on tcgen05 (weights dequantised into shared memory) unless pinned to the mma.sync kernel.
+    # M > 8 runs on tcgen05 (weights dequantised into tensor memory) unless pinned to the mma.sync kernel.
     M, N, K, group = case
     if path == "mma":
         monkeypatch.setenv("BTM_FORCE_INT4", "mma")

@@ -66,6 +66,31 @@ def test_same_inputs_twice_give_the_same_bits():
     assert torch.equal(o1, o2)
 
 
+@pytest.mark.gpu
+def test_zero_k_and_padded_rows():
+    import torch
+    L = _lib.lib()
+    # K = 0: the product is all zeros, whatever the output held before
+    a = torch.empty((5, 0), dtype=torch.float32, device="cuda")
+    b = torch.empty((0, 7), dtype=torch.float32, device="cuda")
+    out = torch.full((5, 7), float("nan"), dtype=torch.float32, device="cuda")
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert L.btm_gemm_f32_static(0, st, 5, 7, 0, a.data_ptr(), 1, b.data_ptr(), 7, out.data_ptr(), 7) == _lib.OK, _lib.last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(out, torch.zeros_like(out))
+    # operands that are views of wider matrices (lda > K, ldb > N, ldc > N), output pitch not a multiple of 16 bytes
+    M, N, K = 130, 67, 50
+    big_a = torch.from_numpy(synth.uniform((M, K + 14), -1, 1, 3, 0).astype(np.float32)).cuda()
+    big_b = torch.from_numpy(synth.uniform((K, N + 5), -1, 1, 3, 1).astype(np.float32)).cuda()
+    big_c = torch.full((M, N + 2), float("nan"), dtype=torch.float32, device="cuda")
+    a, b, got = big_a[:, :K], big_b[:, :N], big_c[:, :N]
+    assert _call_static(L, a, b, got) == _lib.OK, _lib.last_error()
+    torch.cuda.synchronize()
+    ref = a.double() @ b.double()
+    assert ((got.double() - ref).norm() / ref.norm()).item() <= TOL
+    assert torch.isnan(big_c[:, N:]).all()  # nothing written past the N columns
+
+
 def test_products_beyond_the_fixed_scratch_are_refused_with_a_clear_message():
     # Argument checks come before any device work, so this needs no GPU.
     L = _lib.lib()
