@@ -84,10 +84,9 @@ int configure_gemm_tc2_kernels();
 int configure_int4_tc_kernels();
 int configure_int4_gemv_kernels();
 int configure_int4_gemv_rows_kernels();
-// Register-resident GEMV (M <= 8). Returns a btm_status, or -1 when the shape is outside what it takes (nothing launched).
-// nb: 128-k blocks per warp, 16 (ten warps per CTA) or 8 (twenty).
+// Register-resident GEMV. Returns a btm_status, or -1 when the shape is outside what it takes (nothing launched).
 int launch_int4_gemv_rows(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
-                          const void *scales, void *out, int nb);
+                          const void *scales, void *out);
 int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const void *act, const void *w, const void *scales, void *out,
                         int *status, int sm_count);
 int launch_gemm_tc2(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,

@@ -807,12 +807,15 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
         if (rc) return rc;
         return check_cuda(cudaGetLastError(), "int4 gemm launch");
     }
-    // M <= 8: the register-resident kernel (int4_gemv_rows.cu) unless the caller pins one of the two kernels below
-    // (BTM_FORCE_GEMV=stream|slab; rows8 selects its twenty-warp form). Shapes it does not take fall through.
+    // Few rows (M <= 3): the register-resident kernel (int4_gemv_rows.cu), 7.2 us against 9.1 us at M = 1 and 8.1 against
+    // 9.2 us at M = 2 on the 11008 x 4096 workload; at M = 4 the two are level (9.5 us) and at M = 8 its per-CTA
+    // activation staging costs more than it gains (12.3 against 11.1 us), so more rows stay on the streaming kernel below. BTM_FORCE_GEMV=regs|stream|slab pins a
+    // kernel (the tests use it to run every kernel on every shape it takes). Shapes a kernel does not take fall through.
     const char *force_gemv = getenv("BTM_FORCE_GEMV");
-    if (!(force_gemv && (!strcmp(force_gemv, "stream") || !strcmp(force_gemv, "slab")))) {
-        const int rc_rows = launch_int4_gemv_rows(st, sm_count, M, N, K, group, act, w, scales, out, (force_gemv && !strcmp(force_gemv, "rows8")) ? 8 : 16);
-        if (rc_rows != -1) return rc_rows;
+    const bool want_regs = force_gemv ? !strcmp(force_gemv, "regs") : M <= 3;
+    if (want_regs) {
+        const int rc_regs = launch_int4_gemv_rows(st, sm_count, M, N, K, group, act, w, scales, out);
+        if (rc_regs != -1) return rc_regs;
     }
     const bool stage_act = M <= 2; // slab kernel: a slab and more than two staged rows do not fit together
     const int npieces = (K / 128 + 1) / 2;

@@ -19,6 +19,10 @@ from .errors import GPUTaskOnCPUBuild, raise_for_status
 _DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
 
 
+def _LIB():
+    return _lib._lib or _lib.lib()
+
+
 def _require_gpu(*tensors: torch.Tensor) -> int:
     if not torch.cuda.is_available():
         raise GPUTaskOnCPUBuild("GPU task cannot be run on CPU build")  # TensorOps.hpp:5-30
@@ -33,8 +37,9 @@ def _require_gpu(*tensors: torch.Tensor) -> int:
     return int(dev)
 
 
-def _stream() -> C.c_void_p:
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+def _stream(dev: int | None = None) -> int:
+    """The calling thread's current CUDA stream of `dev` as a raw handle (what the C ABI takes as void*)."""
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device() if dev is None else dev)
 
 
 def _rowmajor(t: torch.Tensor, name: str) -> None:
@@ -47,7 +52,7 @@ def init(device: int = 0) -> None:
 
 
 def check_device_status(device: int = 0) -> None:
-    raise_for_status(_lib.lib().btm_check_device_status(device, _stream()))
+    raise_for_status(_lib.lib().btm_check_device_status(device, _stream(device)))
 
 
 def matmul_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
@@ -79,10 +84,10 @@ def matmul_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bias: torch.
     ldb = b.stride(0) if K > 1 else max(N, 1)
     ldc = out.stride(0) if M > 1 else max(N, 1)
     if bias is None and not relu:
-        rc = _lib.lib().btm_gemm(dev, _stream(), _DT[a.dtype], M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
+        rc = _lib.lib().btm_gemm(dev, _stream(dev), _DT[a.dtype], M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
                                  out.data_ptr(), ldc)
     else:
-        rc = _lib.lib().btm_gemm_bias_act(dev, _stream(), _DT[a.dtype], M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
+        rc = _lib.lib().btm_gemm_bias_act(dev, _stream(dev), _DT[a.dtype], M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
                                           bias.data_ptr() if bias is not None else None, 1 if relu else 0,
                                           out.data_ptr(), ldc)
     raise_for_status(rc)
@@ -108,7 +113,7 @@ def bmm_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
     sa = a.stride(0) if B > 1 else M * K
     sb = b.stride(0) if B > 1 else K * N
     sc = out.stride(0) if B > 1 else M * N
-    rc = _lib.lib().btm_bmm(dev, _stream(), _DT[a.dtype], B, M, N, K, a.data_ptr(), sa, b.data_ptr(), sb,
+    rc = _lib.lib().btm_bmm(dev, _stream(dev), _DT[a.dtype], B, M, N, K, a.data_ptr(), sa, b.data_ptr(), sb,
                             out.data_ptr(), sc)
     raise_for_status(rc)
 
@@ -116,8 +121,15 @@ def bmm_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
 def matmul_int4_gpu(act: torch.Tensor, w_packed: torch.Tensor, scales: torch.Tensor, out: torch.Tensor,
                     group: int = 128) -> None:
     """out[M,N] (fp16) = act[M,K] (fp16) . dequant(w_packed[N,K/2], scales[N,K/group])^T."""
-    dev = _require_gpu(act, w_packed, scales, out)
-    if act.dtype != torch.float16 or scales.dtype != torch.float16 or out.dtype != torch.float16:
+    # One pass over the operands: this call sits in front of a kernel of a few microseconds (a decoder calls it once
+    # per layer and token), so the guards are written to cost little. Same checks as the other operators.
+    dev = out.device.index
+    f16 = torch.float16
+    if not (act.is_cuda and w_packed.is_cuda and scales.is_cuda and out.is_cuda):
+        _require_gpu(act, w_packed, scales, out)  # raises with the operator boundary's messages
+    if act.device != out.device or w_packed.device != out.device or scales.device != out.device:
+        raise ValueError("Tensors live on different GPUs")
+    if act.dtype != f16 or scales.dtype != f16 or out.dtype != f16:
         raise ValueError("matmul_int4_gpu: activations, scales and output are Float16")
     if w_packed.dtype != torch.uint8:
         raise ValueError("matmul_int4_gpu: packed weights are bytes (two nibbles each)")
@@ -125,12 +137,12 @@ def matmul_int4_gpu(act: torch.Tensor, w_packed: torch.Tensor, scales: torch.Ten
     N = w_packed.shape[0]
     if w_packed.shape != (N, K // 2) or scales.shape != (N, K // group if group else 0) or out.shape != (M, N):
         raise ValueError("matmul_int4_gpu: shape mismatch")
-    for t in (act, w_packed, scales, out):
-        if not t.is_contiguous():
-            raise ValueError("matmul_int4_gpu: tensors must be contiguous")
-    rc = _lib.lib().btm_int4_matmul(dev, _stream(), M, N, K, group, act.data_ptr(), w_packed.data_ptr(),
-                                    scales.data_ptr(), out.data_ptr())
-    raise_for_status(rc)
+    if not (act.is_contiguous() and w_packed.is_contiguous() and scales.is_contiguous() and out.is_contiguous()):
+        raise ValueError("matmul_int4_gpu: tensors must be contiguous")
+    rc = _LIB().btm_int4_matmul(dev, torch._C._cuda_getCurrentRawStream(dev), M, N, K, group, act.data_ptr(), w_packed.data_ptr(),
+                                scales.data_ptr(), out.data_ptr())
+    if rc:
+        raise_for_status(rc)
 
 
 def dequant_int4_gpu(w_packed: torch.Tensor, scales: torch.Tensor, out: torch.Tensor, group: int = 128) -> None:
@@ -139,7 +151,7 @@ def dequant_int4_gpu(w_packed: torch.Tensor, scales: torch.Tensor, out: torch.Te
     K = K2 * 2
     if out.shape != (N, K) or out.dtype != torch.float16 or scales.dtype != torch.float16:
         raise ValueError("dequant_int4_gpu: shape or dtype mismatch")
-    rc = _lib.lib().btm_int4_dequant(dev, _stream(), N, K, group, w_packed.data_ptr(), scales.data_ptr(), out.data_ptr())
+    rc = _lib.lib().btm_int4_dequant(dev, _stream(dev), N, K, group, w_packed.data_ptr(), scales.data_ptr(), out.data_ptr())
     raise_for_status(rc)
 
 
@@ -148,7 +160,7 @@ def unpack_int4_gpu(w_packed: torch.Tensor, out: torch.Tensor) -> None:
     N, K2 = w_packed.shape
     if out.shape != (N, K2 * 2) or out.dtype != torch.int8:
         raise ValueError("unpack_int4_gpu: shape or dtype mismatch")
-    rc = _lib.lib().btm_int4_unpack(dev, _stream(), N, K2 * 2, w_packed.data_ptr(), out.data_ptr())
+    rc = _lib.lib().btm_int4_unpack(dev, _stream(dev), N, K2 * 2, w_packed.data_ptr(), out.data_ptr())
     raise_for_status(rc)
 
 
@@ -163,7 +175,7 @@ def quantize_int4_gpu(w: torch.Tensor, w_packed: torch.Tensor, scales: torch.Ten
     for t in (w, w_packed, scales):
         if not t.is_contiguous():
             raise ValueError("quantize_int4_gpu: tensors must be contiguous")
-    rc = _lib.lib().btm_int4_quantize(dev, _stream(), N, K, group, w.data_ptr(), w_packed.data_ptr(), scales.data_ptr())
+    rc = _lib.lib().btm_int4_quantize(dev, _stream(dev), N, K, group, w.data_ptr(), w_packed.data_ptr(), scales.data_ptr())
     raise_for_status(rc)
 
 
@@ -176,7 +188,7 @@ def convert_gpu(src: torch.Tensor, dst: torch.Tensor) -> None:
     if src.dtype not in _DT or dst.dtype not in _DT:
         from .errors import NotImplementedOp
         raise NotImplementedOp(f"convert_gpu: {src.dtype} -> {dst.dtype} is not supported")
-    rc = _lib.lib().btm_convert(dev, _stream(), _DT[src.dtype], _DT[dst.dtype], src.numel(), src.data_ptr(), dst.data_ptr())
+    rc = _lib.lib().btm_convert(dev, _stream(dev), _DT[src.dtype], _DT[dst.dtype], src.numel(), src.data_ptr(), dst.data_ptr())
     raise_for_status(rc)
 
 

@@ -98,13 +98,13 @@ def test_bad_arguments(btm):
                             torch.zeros((1, 16), dtype=torch.float16, device="cuda"), 128)
 
 
-@pytest.mark.parametrize("path", ["rows", "rows8", "stream", "slab"])
+@pytest.mark.parametrize("path", ["regs", "stream", "slab"])
 @pytest.mark.parametrize("case", [(1, 11008, 4096, 128), (8, 11008, 4096, 128), (3, 100, 4096, 128), (2, 37, 2048, 128),
                                   (1, 48, 2304, 128), (5, 16, 8192, 256), (2, 3000, 4096, 128), (4, 5000, 1024, 128), (7, 129, 11008, 128),
-                                  (8, 40, 12288, 512), (6, 2049, 640, 128)])
+                                  (8, 40, 12288, 512), (6, 2049, 640, 128), (4, 11008, 4096, 128), (1, 700, 512, 128), (3, 31, 3584, 128)])
 def test_gemv_both_kernels(btm, oracle, case, path, monkeypatch):
-    # M <= 8: the register-resident kernel (ten or twenty warps per CTA), or pinned to the persistent streaming
-    # kernel or to the kernel that stages one whole 16-row slab per CTA.
+    # M <= 8 pinned to each of the three kernels: register-resident (the default up to four rows), persistent streaming
+    # (the default above), one whole 16-row slab per CTA. A kernel that does not take a shape hands it on.
     M, N, K, group = case
     monkeypatch.setenv("BTM_FORCE_GEMV", path)
     w, packed, s, act = make(M, N, K, group, 23 + M + N)
