@@ -36,6 +36,13 @@ SIGNATURES = {
     "btm_convert": (_i, [_i, _vp, _i, _i, _i64, _vp, _vp]),
     "btm_int4_unpack": (_i, [_i, _vp, _i, _i, _vp, _vp]),
     "btm_gemm_nshard": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, C.POINTER(_vp), _i64, _i, _i]),
+    "btm_gemm_nshard_mc": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i, _i]),
+    "btm_mc_supported": (_i, [_i]),
+    "btm_mc_create": (_i, [_i, _i, _sz, C.POINTER(_vp), C.POINTER(_i)]),
+    "btm_mc_import": (_i, [_i, _i, _sz, _i, C.POINTER(_vp)]),
+    "btm_mc_add_device": (_i, [_vp]),
+    "btm_mc_bind": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
+    "btm_mc_release": (_i, [_vp]),
     "btm_replicate_rows": (_i, [_i, _vp, C.POINTER(_vp), _i, _i, _sz, _sz]),
     "btm_ipc_alloc": (_i, [_i, _sz, C.POINTER(_vp), C.c_char_p]),
     "btm_ipc_open": (_i, [_i, C.c_char_p, C.POINTER(_vp)]),

@@ -176,6 +176,7 @@ struct GemmCall {
     long long lda, ldb, strideA, strideB;
     void *C[kMaxDst];
     int ndst;
+    void *mc; // multicast mapping of C, or NULL
     long long ldc, strideC, col0;
     const void *bias; // optional, one value per column of this launch's N
     int act;          // 0 none, 1 ReLU
@@ -222,6 +223,7 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
     fill_wait_params(&p);
     p.bias = c.bias;
     p.act = c.act;
+    p.mc = c.mc;
     if (c.ndst > 1) {
         // Peer stores of a tile are spread over part of the next tile's main loop instead of leaving the
         // SM as one burst. Unit: SM cycles per 64-deep k-block (a k-block of a 256 x 256 pair tile takes
@@ -513,6 +515,33 @@ int btm_gemm_nshard(int device, void *stream, int dtype, int M, int Nloc, int K,
     c.C[0] = C_ranks[rank];
     for (int i = 1; i < nranks; ++i) c.C[i] = C_ranks[(rank + i) % nranks];
     c.ndst = nranks; c.ldc = ldc; c.col0 = (long long)rank * Nloc;
+    return run_16bit(ds, (cudaStream_t)stream, c);
+}
+
+int btm_gemm_nshard_mc(int device, void *stream, int dtype, int M, int Nloc, int K, const void *A, int64_t lda, const void *B_local,
+                       int64_t ldb, void *C_local, void *C_multicast, int64_t ldc, int rank, int nranks)
+{
+    if (dtype != BTM_F16 && dtype != BTM_BF16)
+        return set_error(BTM_ERR_UNSUPPORTED, "sharded matmul: dtype %d is not supported (Float16, BFloat16 only)", dtype);
+    if (nranks < 1 || nranks > kMaxDst || rank < 0 || rank >= nranks)
+        return set_error(BTM_ERR_INVALID, "sharded matmul: rank %d of %d is out of range (at most %d ranks)", rank, nranks, kMaxDst);
+    if (!C_multicast || !C_local) return set_error(BTM_ERR_INVALID, "sharded matmul: null output mapping");
+    if (ldc < (int64_t)Nloc * nranks) return set_error(BTM_ERR_INVALID, "sharded matmul: ldc=%lld is smaller than nranks*Nloc", (long long)ldc);
+    int rc = check_gemm_args(dtype, M, Nloc, K, A, lda, B_local, ldb, C_local, ldc);
+    if (rc) return rc;
+    // The multimem stores are 16 bytes wide and unpredicated inside a chunk of 8 columns, and the operands must be
+    // addressable by the tensor-core kernels (there is no general-kernel form of the multicast epilogue).
+    if (K <= 0 || (Nloc % 8) || (ldc % 8) || (((uintptr_t)C_multicast | (uintptr_t)C_local) & 15) || !tma_ok(A, lda, 0, 1, 2) || !tma_ok(B_local, ldb, 0, 1, 2))
+        return set_error(BTM_ERR_UNSUPPORTED, "sharded matmul over multicast memory: needs K > 0, Nloc and ldc multiples of 8, 16-byte aligned operands");
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    if (M == 0 || Nloc == 0) return BTM_OK;
+    GemmCall c;
+    memset(&c, 0, sizeof(c));
+    c.dtype = dtype; c.batch = 1; c.M = M; c.N = Nloc; c.K = K;
+    c.A = A; c.B = B_local; c.lda = lda; c.ldb = ldb;
+    c.C[0] = C_local; c.ndst = 1; c.mc = C_multicast;
+    c.ldc = ldc; c.col0 = (long long)rank * Nloc;
     return run_16bit(ds, (cudaStream_t)stream, c);
 }
 

@@ -26,6 +26,7 @@ struct GemmParams {
     long long ldc;     // elements
     long long strideC; // elements between products
     long long col0;    // first output column of this launch inside C
+    void *mc;          // multicast mapping of C (one multimem store reaches every rank's copy), or NULL
     int pace_cycles;   // >0: peer stores of one tile are spread over this many SM cycles (several destinations only)
     const void *bias;  // optional: one value per output column (same dtype as C), added to the fp32 accumulator before rounding
     int act;           // 0 none, 1 ReLU (after the bias)

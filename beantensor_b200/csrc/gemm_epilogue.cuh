@@ -45,6 +45,14 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// 16 bytes to a multicast address: the switch writes them at the same offset of every memory bound to the object.
+__device__ __forceinline__ void multimem_st_v4(void *mc_addr, const uint4 &v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
 template <int DT>
 __device__ __forceinline__ void pack16(const uint32_t (&acc)[32], uint32_t (&packed)[16])
 {
@@ -146,7 +154,9 @@ __device__ __forceinline__ void epilogue_band_multi(const GemmParams &p, const S
         fence_proxy_async_smem();
         __syncwarp();
         const int col = col_first + c * 128;
-        if (lane == 0) {
+        // With a multicast mapping the local copy is written by the same multimem stores as the peers' (this device
+        // is a member of the object), so the staging tiles only serve the transposition below.
+        if (lane == 0 && p.mc == nullptr) {
             if (row0 < p.M && col < p.N) tma_store_3d(&cmaps.m[0], epi_smem, (int)p.col0 + col, row0, batch);
             if (row0 < p.M && col + 64 < p.N) tma_store_3d(&cmaps.m[0], epi_smem + EPI_TILE_BYTES, (int)p.col0 + col + 64, row0, batch);
             bulk_commit();
@@ -162,6 +172,17 @@ __device__ __forceinline__ void epilogue_band_multi(const GemmParams &p, const S
         }
         const int ccol = col + chunk * 8; // first of this lane's 8 columns
         const long long base = (long long)batch * p.strideC + p.col0 + ccol;
+        if (p.mc != nullptr) {
+            // One outbound copy: 16-byte multimem stores, two rows x 256 contiguous bytes per warp instruction. The
+            // launcher guarantees that N is a multiple of 8 here, so a lane's 8 columns are all inside or all outside.
+            uint16_t *dst = reinterpret_cast<uint16_t *>(p.mc);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int row = row0 + 2 * i + (lane >> 4);
+                if (row < p.M && ccol + 8 <= p.N) multimem_st_v4(dst + base + (long long)row * p.ldc, regs[i]);
+            }
+            continue;
+        }
         for (int d = 1; d < p.ndst; ++d, ++batch_no) {
             uint16_t *dst = reinterpret_cast<uint16_t *>(p.C[d]);
             if (step > 0) {
@@ -214,7 +235,7 @@ __device__ __forceinline__ void epilogue_band(const GemmParams &p, const StoreMa
     }
     const uint32_t swz = (uint32_t)(lane & 7);
     if constexpr (DT != BTM_F32) {
-        if (p.ndst > 1 && (bn & 127) == 0) {
+        if ((p.ndst > 1 || p.mc != nullptr) && (bn & 127) == 0) {
             epilogue_band_multi<DT>(p, cmaps, tmem_band, row0, col_first, bn, batch, epi_smem, tile_count, lane);
             return;
         }

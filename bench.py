@@ -262,8 +262,7 @@ METRIC_MULTI = "bf16 GEMM TFLOP/s (M=N=K=16384, B sharded by N-columns, all-gath
 
 
 def workload_multi(world):
-    return (f"bf16 GEMM M=N=K=16384, B split by N-columns over {world} ranks, all-gather of C fused into the epilogue "
-            "(peer stores over NVLink)")
+    return f"bf16 GEMM M=N=K=16384, B split by N-columns over {world} ranks, all-gather of C fused into the epilogue (stores over NVLink)"
 
 
 def cpu_gemm_sample(n: int, target_seconds: float, max_rows: int = 4096):
@@ -718,10 +717,31 @@ def run_multi(args, peaks):
     del b_full
     torch.cuda.empty_cache()
 
-    # ---- the sharded product with the all-gather fused into the epilogue
-    def step(i):
+    # ---- the sharded product with the all-gather fused into the epilogue. Two forms of the peer leg: multimem stores
+    # to an NVSwitch multicast mapping of C (one outbound copy per tile; used when every rank's device supports it), or
+    # plain stores to each peer's copy in turn. The one that is not timed as the headline is timed as a comparator.
+    from beantensor_b200 import multicast
+    mcb, mc_note = None, None
+    if not args.no_multicast:
+        try:
+            mcb = multicast.MulticastBuffer(dist, local_rank, rank, world, n * n * 2)
+        except NotImplementedError as e:
+            mc_note = str(e)
+    else:
+        mc_note = "switched off by --no-multicast"
+
+    def step_peer(i):
         raise_for_status(L.btm_gemm_nshard(local_rank, stream, _lib.BF16, n, nloc, n, a.data_ptr(), n, b_block.data_ptr(), nloc,
                                            c_buf.table, n, rank, world))
+
+    def step_mc(i):
+        raise_for_status(L.btm_gemm_nshard_mc(local_rank, stream, _lib.BF16, n, nloc, n, a.data_ptr(), n, b_block.data_ptr(), nloc,
+                                              mcb.local_ptr, mcb.mc_ptr, n, rank, world))
+
+    step = step_mc if mcb is not None else step_peer
+    if mcb is not None:
+        c_dev = _wrap_device_memory(torch, mcb.local_ptr, (n, n)).view(dtype)
+    collective = "multimem stores to an NVSwitch multicast mapping of C" if mcb is not None else "plain stores to every peer's copy of C"
 
     ms_list, t0, t1 = time_reps(torch, dist, world, step, args.steps, args.warmup, args.min_span, 100)
     ops.check_device_status(local_rank)
@@ -729,6 +749,10 @@ def run_multi(args, peaks):
     sp = spread(ms_list, args.steps)
     ms_step = sp["ms_per_step_median"]
     tflops = flops / (ms_step * 1e-3) / 1e12
+    other = None
+    if mcb is not None:
+        o_ms, _, _ = time_reps(torch, dist, world, step_peer, 5, 3, 0.1, 20)
+        other = {"what": "the same product with plain peer stores instead of multimem stores", "ms_per_step": statistics.median(o_ms) / 5}
 
     # ---- parity of the gathered C (outside the timed region): a fresh product into a cleared C
     c_dev.fill_(float("nan"))
@@ -821,7 +845,7 @@ def run_multi(args, peaks):
             "metric": METRIC_MULTI, "value": tflops, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded 4096^2 blocks tiled)",
-            "config": {"workload": workload_multi(world), "l2": "inputs (1 GiB+) exceed L2", "parallelism": f"nshard{world}",
+            "config": {"workload": workload_multi(world), "collective": collective, "multicast_note": mc_note, "l2": "inputs (1 GiB+) exceed L2", "parallelism": f"nshard{world}",
                        "timing": f"{sp['regions']} regions of exactly {args.steps} steps back to back, max over ranks per region; value is the "
                                  "median region"},
             "timing": sp,
@@ -832,6 +856,7 @@ def run_multi(args, peaks):
             "parity_check": parity,
             "roofline": roof,
             "nccl_comparator": comparator,
+            "peer_store_comparator": other,
             "cpu_baseline": None,
             "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": panel_bytes + n * nloc * 2, "d2h_bytes_per_step": n * nloc * 2,
                     "steps": e2e_steps, "bytes_are": "per rank", "result_checked": e2e_ok,
@@ -842,6 +867,8 @@ def run_multi(args, peaks):
             "configs": bmm_records,
         }
         print(json.dumps(line), flush=True)
+    if mcb is not None:
+        mcb.release()
     c_buf.release()
     a_buf.release()
     dist.destroy_process_group()
@@ -871,6 +898,7 @@ def main():
     ap.add_argument("--force-kernel", default=None, choices=["1cta", "2cta"],
                     help="pin the 16-bit matmul to the one-CTA or the two-SM kernel (default: the library chooses)")
     ap.add_argument("--size", type=int, default=4096, help="M=N=K of the headline product (profiling aid; the metric is quoted at 4096)")
+    ap.add_argument("--no-multicast", action="store_true", help="N > 1: keep the all-gather on plain peer stores")
     ap.add_argument("--min-span", type=float, default=0.6,
                     help="seconds the repeated timed regions should cover, so that clock samples fall inside (0: one region)")
     args = ap.parse_args()

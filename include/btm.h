@@ -227,6 +227,35 @@ int btm_int4_unpack(int device, void *stream, int N, int K, const void *w_packed
 int btm_gemm_nshard(int device, void *stream, int dtype, int M, int Nloc, int K, const void *A, int64_t lda,
                     const void *B_local, int64_t ldb, void *const *C_ranks, int64_t ldc, int rank, int nranks);
 
+/* The same product with ONE outbound copy per tile instead of nranks - 1: every rank's C lives in memory bound to one
+ * NVSwitch multicast object (btm_mc_* below), `C_multicast` is this rank's mapping of that object and `C_local` its
+ * ordinary mapping of its own copy. The epilogue writes each finished tile with multimem stores to `C_multicast`; the
+ * switch delivers it to all copies, this rank's included. Stores only: nothing is ever loaded through the multicast
+ * mapping. BTM_ERR_UNSUPPORTED (nothing launched) unless K > 0, Nloc and ldc are multiples of 8 and the operands are
+ * 16-byte aligned; callers fall back to btm_gemm_nshard. The caller provides the cross-rank barrier before C is read. */
+int btm_gemm_nshard_mc(int device, void *stream, int dtype, int M, int Nloc, int K, const void *A, int64_t lda,
+                       const void *B_local, int64_t ldb, void *C_local, void *C_multicast, int64_t ldc, int rank, int nranks);
+
+/* Multicast memory for btm_gemm_nshard_mc, one process per GPU. No counterpart in the reference (its one multi-GPU
+ * primitive is a whole-tensor peer copy, Tensor/TensorOps.cu:282-313).
+ *   btm_mc_supported  1 if `device` can be a member of a multicast object, else 0.
+ *   btm_mc_create     (one rank) creates the object for `nranks` devices and `bytes` per device and returns a POSIX
+ *                     file descriptor for it; the caller passes that descriptor to the other processes (SCM_RIGHTS
+ *                     over a Unix-domain socket) and closes its copy afterwards.
+ *   btm_mc_import     (the other ranks) opens the object from the received descriptor.
+ *   btm_mc_add_device (every rank) adds its device to the object. The caller then makes sure that EVERY rank has
+ *                     done so successfully before any rank goes on, because a bind waits for the whole team.
+ *   btm_mc_bind       (every rank) allocates `bytes` of its own memory, binds it at offset 0 and maps both.
+ *                     Returns the two mappings.
+ *   btm_mc_release    (every rank, behind a barrier, while all ranks are alive) unmaps, unbinds and frees. */
+typedef struct btm_mc btm_mc;
+int btm_mc_supported(int device);
+int btm_mc_create(int device, int nranks, size_t bytes, btm_mc **out, int *export_fd);
+int btm_mc_import(int device, int nranks, size_t bytes, int fd, btm_mc **out);
+int btm_mc_add_device(btm_mc *h);
+int btm_mc_bind(btm_mc *h, void **local_ptr, void **mc_ptr);
+int btm_mc_release(btm_mc *h);
+
 /* Placement helper for an operand that every rank needs whole (A of the N-sharded product) when each rank has
  * only a slice of it at hand: `bufs[r]` is rank r's copy of the operand (peer-mapped, as for btm_gemm_nshard), and the
  * byte range [offset_bytes, offset_bytes + bytes) of this rank's copy is sent to the same range of every other

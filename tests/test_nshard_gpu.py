@@ -131,3 +131,98 @@ def test_real_ranks_over_peer_memory(oracle):
         assert p.exitcode == 0
     for rank, err in results:
         assert err <= TOL[_lib.BF16], (rank, err)
+
+
+def _rank_main_multicast(rank, world, port, q):
+    # The same product with the output in NVSwitch multicast memory: one multimem store per tile reaches every rank.
+    # No rank leaves while memory is bound: results travel through the queue only after release().
+    sys.path.insert(0, ROOT)
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    import torch
+    import torch.distributed as dist
+    from beantensor_b200 import multicast, ops
+    from oracle import oracle as O
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    result = (rank, "error", "did not finish")
+    try:
+        ops.init(rank)
+        L = _lib.lib()
+        dtype = _lib.BF16
+        M, N, K = 384, 256 * world, 320
+        A, B = gemm_inputs(dtype, M, N, K, 35)
+        c0, c1 = sharding.column_block(N, rank, world)
+        a = to_gpu(A, dtype)
+        b_loc = to_gpu(np.ascontiguousarray(B[:, c0:c1]), dtype)
+        try:
+            buf = multicast.MulticastBuffer(dist, rank, rank, world, M * N * 2)
+        except NotImplementedError as e:
+            result = (rank, "unsupported", str(e))
+            buf = None
+        if buf is not None:
+            err, rc = float("inf"), _lib.OK
+            try:
+                class Raw:
+                    __cuda_array_interface__ = {"shape": (M, N), "typestr": "<i2", "data": (buf.local_ptr, False), "version": 2}
+
+                c_local = torch.as_tensor(Raw(), device="cuda")
+                c_local.fill_(-1)
+                torch.cuda.synchronize()
+                dist.barrier()
+                st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+                rc = L.btm_gemm_nshard_mc(rank, st, dtype, M, c1 - c0, K, a.data_ptr(), K, b_loc.data_ptr(), c1 - c0,
+                                          buf.local_ptr, buf.mc_ptr, N, rank, world)
+                msg = _lib.last_error() if rc else ""
+                torch.cuda.synchronize()
+                dist.barrier()
+                torch.cuda.synchronize()
+                if rc == _lib.OK:
+                    ops.check_device_status(rank)
+                    got = c_local.cpu().numpy().view(np.uint16)
+                    err = O.rel_frobenius(got, dtype, O.gemm(dtype, A, B))
+                    result = (rank, "ok", float(err))
+                else:
+                    result = (rank, "error", msg)
+            finally:
+                buf.release()
+    except Exception as e:  # reported through the queue; the process still leaves in order
+        result = (rank, "error", repr(e))
+    finally:
+        q.put(result)
+        dist.destroy_process_group()
+
+
+def test_real_ranks_over_multicast_memory(oracle):
+    import torch
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main_multicast, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    if all(kind == "unsupported" for _, kind, _ in results):
+        pytest.skip("multicast objects are not available here: " + str(results[0][2]))
+    for rank, kind, val in results:
+        assert kind == "ok", (rank, kind, val)
+        assert val <= TOL[_lib.BF16], (rank, val)
+
+
+def test_multicast_entry_refuses_what_it_cannot_store(btm):
+    L = _lib.lib()
+    p = C.c_void_p(256)
+    # Nloc not a multiple of 8: the 16-byte multimem stores could not be clipped
+    assert L.btm_gemm_nshard_mc(0, None, _lib.F16, 8, 12, 64, p, 64, p, 12, p, p, 24, 0, 2) == _lib.ERR_UNSUPPORTED
+    assert L.btm_gemm_nshard_mc(0, None, _lib.F32, 8, 8, 64, p, 64, p, 8, p, p, 16, 0, 2) == _lib.ERR_UNSUPPORTED
+    assert L.btm_gemm_nshard_mc(0, None, _lib.F16, 8, 8, 64, p, 64, p, 8, None, p, 16, 0, 2) == _lib.ERR_INVALID
