@@ -33,9 +33,18 @@ constexpr int BN = 256;           // full tile width
 constexpr int BKE = 64;           // k elements per stage (128 bytes)
 constexpr int A_BYTES = CTA_M * 128;
 constexpr int CHUNK_BYTES = BKE * 128; // one 64-column B chunk: 64 k-rows x 128 B
-constexpr int STAGE_BYTES = A_BYTES + 2 * CHUNK_BYTES; // 16 KB + 16 KB
+constexpr int KB_BYTES = A_BYTES + 2 * CHUNK_BYTES; // one 64-deep k-block of a CTA: 16 KB of A + 16 KB of B
+// k-blocks per pipeline stage: a stage is handed over (one full / empty barrier round trip, one commit) per KPS
+// k-blocks, i.e. per 4 * KPS tcgen05.mma. Measured at fp16 4096^3 under the power cap, same run as the library's
+// kernel on the same buffers: KPS 1 (six stages of 32 KB) 1076 TFLOP/s = 0.89 of the library, KPS 2 (three stages of
+// 64 KB) 1132 = 0.95, KPS 3 (two stages of 96 KB) 1047 = 0.875.
+#ifndef BTM_TC2_KPS
+#define BTM_TC2_KPS 2
+#endif
+constexpr int KPS = BTM_TC2_KPS;
+constexpr int STAGE_BYTES = KPS * KB_BYTES;
 #ifndef BTM_TC2_STAGES
-#define BTM_TC2_STAGES 6
+#define BTM_TC2_STAGES (6 / BTM_TC2_KPS)
 #endif
 constexpr int STAGES = BTM_TC2_STAGES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_SMEM_BYTES + 1024; // ring + epilogue staging + alignment slack
@@ -145,19 +154,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int half_bn = pt.bn >> 1;      // columns of B this CTA loads
                 const int chunks = half_bn >> 6;     // 64-column chunks: 2 or 1
                 const uint32_t cta_bytes = (uint32_t)(A_BYTES + chunks * CHUNK_BYTES);
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = 0; kb < p.num_kb; kb += KPS) {
                     if (!mbar_wait<true>(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY, p.wait_limit)) {
                         ok = false;
                         break;
                     }
+                    const int nsub = min(KPS, p.num_kb - kb); // k-blocks in this stage (the last stage of a tile may be short)
                     const uint32_t full_local = smem_u32(&bar_full[stage]);
-                    if (rank == 0) mbar_expect_tx(full_local, 2u * cta_bytes);
+                    if (rank == 0) mbar_expect_tx(full_local, 2u * cta_bytes * (uint32_t)nsub);
                     const uint32_t full_leader = map_to_cta(full_local, 0);
-                    const uint32_t sbase = smem_base + stage * STAGE_BYTES;
-                    const int k0 = kb * BKE;
-                    tma_load_3d_2sm(sbase, &tmA, k0, pt.m * PAIR_M + (int)rank * CTA_M, pt.b, full_leader);
-                    for (int c = 0; c < chunks; ++c)
-                        tma_load_3d_2sm(sbase + A_BYTES + c * CHUNK_BYTES, &tmB, pt.n0 + (int)rank * half_bn + c * 64, k0, pt.b, full_leader);
+                    for (int sub = 0; sub < nsub; ++sub) {
+                        const uint32_t sbase = smem_base + stage * STAGE_BYTES + sub * KB_BYTES;
+                        const int k0 = (kb + sub) * BKE;
+                        tma_load_3d_2sm(sbase, &tmA, k0, pt.m * PAIR_M + (int)rank * CTA_M, pt.b, full_leader);
+                        for (int c = 0; c < chunks; ++c)
+                            tma_load_3d_2sm(sbase + A_BYTES + c * CHUNK_BYTES, &tmB, pt.n0 + (int)rank * half_bn + c * 64, k0, pt.b, full_leader);
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -183,18 +195,21 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!mbar_wait<true>(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag, p.status, WAIT_MMA_TMEM_EMPTY, p.wait_limit)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = 0; kb < p.num_kb; kb += KPS) {
                     if (!mbar_wait<true>(smem_u32(&bar_full[stage]), phase, &abort_flag, p.status, WAIT_MMA_FULL, p.wait_limit)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a0 = smem_base + stage * STAGE_BYTES, b0 = a0 + A_BYTES;
+                    const int nsub = min(KPS, p.num_kb - kb);
+                    for (int sub = 0; sub < nsub; ++sub) {
+                        const uint32_t a0 = smem_base + stage * STAGE_BYTES + sub * KB_BYTES, b0 = a0 + A_BYTES;
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t ad = make_smem_desc_sw128(a0 + ks * 32, 16, 1024);
-                        const uint64_t bd = make_smem_desc_sw128(b0 + ks * 16 * 128, CHUNK_BYTES, 1024);
-                        umma<2, false>(d_tmem, ad, bd, idesc, (uint32_t)((kb | ks) != 0));
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const uint64_t ad = make_smem_desc_sw128(a0 + ks * 32, 16, 1024);
+                            const uint64_t bd = make_smem_desc_sw128(b0 + ks * 16 * 128, CHUNK_BYTES, 1024);
+                            umma<2, false>(d_tmem, ad, bd, idesc, (uint32_t)((kb | sub | ks) != 0));
+                        }
                     }
                     umma_commit_2sm(smem_u32(&bar_empty[stage]), (uint16_t)3);
                     if (++stage == STAGES) {
