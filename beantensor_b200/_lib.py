@@ -26,6 +26,7 @@ SIGNATURES = {
     "btm_gemm": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
     "btm_gemm_bias_act": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i, _vp, _i64]),
     "btm_gemm_bt": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "btm_gemm_strided": (_i, [_i, _vp, _i, _i, _i, _i, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64]),
     "btm_gemm_f32_workspace_bytes": (_sz, [_i, _i, _i]),
     "btm_gemm_f32_ws": (_i, [_i, _vp, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _sz]),
     "btm_gemm_f32_static": (_i, [_i, _vp, _i, _i, _i, _vp, _i64, _vp, _i64, _vp, _i64]),

@@ -252,6 +252,8 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
     return launch_gemm_tc(c.dtype, st, ds->sm_count, tmA, tmB, cm, p, 0);
 }
 
+static int run_f32_planes(DeviceState *ds, cudaStream_t st, const GemmCall &c, float *a_hi, float *b_hi, long long Kp);
+
 static int run_f32(DeviceState *ds, cudaStream_t st, const GemmCall &c, void *ws, size_t ws_bytes)
 {
     // Operand planes in scratch: A_hi, A_lo [M, Kp] then B^T_hi, B^T_lo [N, Kp], pitch padded to 4 floats.
@@ -264,6 +266,14 @@ static int run_f32(DeviceState *ds, cudaStream_t st, const GemmCall &c, void *ws
     float *a_hi = (float *)ws, *a_lo = a_hi + a_plane, *b_hi = a_lo + a_plane, *b_lo = b_hi + b_plane;
     int rc = launch_split_tf32_pair(st, (const float *)c.A, c.lda, c.M, c.K, a_hi, a_lo, (const float *)c.B, c.ldb, c.N, b_hi, b_lo, Kp);
     if (rc) return rc;
+    return run_f32_planes(ds, st, c, a_hi, b_hi, Kp);
+}
+
+// The product kernel on prepared operand planes: A_hi, A_lo [M, Kp] from a_hi on, B^T_hi, B^T_lo [N, Kp] from b_hi on.
+static int run_f32_planes(DeviceState *ds, cudaStream_t st, const GemmCall &c, float *a_hi, float *b_hi, long long Kp)
+{
+    const size_t a_plane = (size_t)c.M * Kp, b_plane = (size_t)c.N * Kp;
+    int rc = BTM_OK;
     // The B box is one whole tile (bn rows), so the tile width is chosen here: 128 columns, or 64
     // when that leaves SMs without a tile.
     const long long t128 = (long long)((c.M + 127) / 128) * ((c.N + 127) / 128);
@@ -488,6 +498,81 @@ int btm_gemm_bt(int device, void *stream, int dtype, int M, int N, int K, const 
     rc = encode_store_maps(&cm, dtype, p);
     if (rc) return rc;
     return launch_gemm_tc_bt(dtype, st, ds->sm_count, tmA, tmB, cm, p, bn);
+}
+
+int btm_gemm_strided(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t a_rs, int64_t a_cs, const void *B,
+                     int64_t b_rs, int64_t b_cs, void *C, int64_t ldc)
+{
+    if (dtype != BTM_F16 && dtype != BTM_BF16 && dtype != BTM_F32)
+        return set_error(BTM_ERR_UNSUPPORTED, "matmul: dtype %d is not supported (Float16, BFloat16, Float32 only)", dtype);
+    if (M < 0 || N < 0 || K < 0) return set_error(BTM_ERR_INVALID, "matmul: negative dimension (M=%d N=%d K=%d)", M, N, K);
+    if (a_rs < 0 || a_cs < 0 || b_rs < 0 || b_cs < 0) return set_error(BTM_ERR_INVALID, "matmul: negative strides are not supported");
+    // Row-major operands are the plain product.
+    if ((a_cs == 1 || K <= 1) && (b_cs == 1 || N <= 1))
+        return btm_gemm(device, stream, dtype, M, N, K, A, M > 1 ? a_rs : std::max<int64_t>(K, 1), B, K > 1 ? b_rs : std::max<int64_t>(N, 1), C, ldc);
+    if (M > 0 && N > 0 && !C) return set_error(BTM_ERR_INVALID, "matmul: null output pointer");
+    if ((M > 0 && K > 0 && !A) || (K > 0 && N > 0 && !B)) return set_error(BTM_ERR_INVALID, "matmul: null operand pointer");
+    if (ldc < N) return set_error(BTM_ERR_INVALID, "matmul: ldc=%lld is smaller than N=%d", (long long)ldc, N);
+    const size_t es = es_of(dtype);
+    if (((uintptr_t)A % es) || ((uintptr_t)B % es) || ((uintptr_t)C % es)) return set_error(BTM_ERR_INVALID, "matmul: pointer not aligned to the element size");
+    DeviceState *ds = device_state(device);
+    if (!ds) return last_code();
+    if (M == 0 || N == 0) return BTM_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    // Which operand is stored transposed (unit stride along the other index)? Anything else takes the general kernel.
+    const bool a_row = a_cs == 1 || K <= 1, a_t = !a_row && (a_rs == 1 || M <= 1);
+    const bool b_row = b_cs == 1 || N <= 1, b_t = !b_row && (b_rs == 1 || K <= 1);
+    const bool unit = (a_row || a_t) && (b_row || b_t);
+    if (dtype == BTM_F32 && unit && K > 0) {
+        // The split pass rewrites both operands anyway: it reads them in whatever order they are stored.
+        const long long Kp = (K + 3) & ~3LL;
+        const size_t a_plane = (size_t)M * Kp, b_plane = (size_t)N * Kp, need = (2 * a_plane + 2 * b_plane) * sizeof(float);
+        void *ws = nullptr;
+        int rc = check_cuda(cudaMallocFromPoolAsync(&ws, need, ds->pool, st), "cudaMallocFromPoolAsync(fp32 split scratch)");
+        if (rc) return rc;
+        float *a_hi = (float *)ws, *a_lo = a_hi + a_plane, *b_hi = a_lo + a_plane, *b_lo = b_hi + b_plane;
+        rc = a_t ? launch_split_tf32_transpose(st, (const float *)A, a_cs, K, M, a_hi, a_lo, Kp)
+                 : launch_split_tf32(st, (const float *)A, a_rs, M, K, a_hi, a_lo, Kp);
+        if (!rc)
+            rc = b_t ? launch_split_tf32(st, (const float *)B, b_cs, N, K, b_hi, b_lo, Kp)
+                     : launch_split_tf32_transpose(st, (const float *)B, b_rs, K, N, b_hi, b_lo, Kp);
+        if (!rc) {
+            GemmCall c;
+            memset(&c, 0, sizeof(c));
+            c.dtype = BTM_F32; c.batch = 1; c.M = M; c.N = N; c.K = K;
+            c.C[0] = C; c.ndst = 1; c.ldc = ldc;
+            rc = run_f32_planes(ds, st, c, a_hi, b_hi, Kp);
+        }
+        const int rc_free = check_cuda(cudaFreeAsync(ws, st), "cudaFreeAsync(fp32 split scratch)");
+        return rc ? rc : rc_free;
+    }
+    if (dtype != BTM_F32 && unit && K > 0) {
+        const long long lda = a_t ? a_cs : a_rs, ldb = b_t ? b_cs : b_rs;
+        if (tma_ok(A, lda, 0, 1, es) && tma_ok(B, ldb, 0, 1, es)) {
+            const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+            const int bn = t256 < ds->sm_count ? 128 : 256;
+            CUtensorMap tmA, tmB;
+            int rc = a_t ? encode_tmap_3d(&tmA, dtype, A, (uint64_t)M, (uint64_t)K, 1, (uint64_t)lda * es, (uint64_t)lda * es, 64, 64)
+                         : encode_tmap_3d(&tmA, dtype, A, (uint64_t)K, (uint64_t)M, 1, (uint64_t)lda * es, (uint64_t)lda * es, 64, 128);
+            if (rc) return rc;
+            rc = b_t ? encode_tmap_3d(&tmB, dtype, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb * es, (uint64_t)ldb * es, 64, (uint32_t)bn)
+                     : encode_tmap_3d(&tmB, dtype, B, (uint64_t)N, (uint64_t)K, 1, (uint64_t)ldb * es, (uint64_t)ldb * es, 64, 64);
+            if (rc) return rc;
+            GemmParams p;
+            memset(&p, 0, sizeof(p));
+            p.M = M; p.N = N; p.K = K; p.batch = 1; p.group_m = 8; p.ndst = 1;
+            p.C[0] = C; p.ldc = ldc;
+            p.c_vec_ok = (aligned16(C) && (ldc * (long long)es) % 16 == 0) ? 1 : 0;
+            p.status = ds->status;
+            fill_wait_params(&p);
+            StoreMaps cm;
+            rc = encode_store_maps(&cm, dtype, p);
+            if (rc) return rc;
+            return launch_gemm_tc_layout(dtype, st, ds->sm_count, tmA, tmB, cm, p, bn, a_t, b_t);
+        }
+    }
+    // Arbitrary strides, unaligned transposed operands, K == 0: the general kernel, same arithmetic contract.
+    return launch_gemm_simt(dtype, st, 1, M, N, K, A, a_rs, 0, B, b_rs, 0, C, ldc, 0, nullptr, 0, a_cs, b_cs);
 }
 
 int btm_gemm_nshard(int device, void *stream, int dtype, int M, int Nloc, int K, const void *A, int64_t lda,

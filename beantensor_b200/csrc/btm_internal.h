@@ -64,10 +64,12 @@ int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &
                    const GemmParams &p, int force_bn);
 int launch_gemm_tc_bt(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
                       const GemmParams &p, int bn);
-// bias / act: see GemmParams.
+int launch_gemm_tc_layout(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
+                          const GemmParams &p, int bn, bool a_t, bool b_t);
+// bias / act: see GemmParams. a_cs / b_cs: element stride between consecutive columns of A / B (1 = row-major).
 int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K, const void *A, long long lda,
                      long long strideA, const void *B, long long ldb, long long strideB, void *C, long long ldc,
-                     long long strideC, const void *bias = nullptr, int act = 0);
+                     long long strideC, const void *bias = nullptr, int act = 0, long long a_cs = 1, long long b_cs = 1);
 int launch_split_tf32(cudaStream_t st, const float *src, long long ld, int rows, int cols, float *dst_hi,
                       float *dst_lo, long long ld_dst);
 int launch_split_tf32_pair(cudaStream_t st, const float *A, long long lda, int M, int K, float *a_hi, float *a_lo, const float *B,

@@ -1,6 +1,6 @@
-// General CUDA-core matmul: the same contract as the tensor-core kernels (row-major operands,
-// fp32 accumulation, round-to-nearest-even output) for shapes and pointers that TMA cannot
-// address (row pitch or base not 16-byte aligned, K == 0). Any M, N, K and any alignment.
+// General CUDA-core matmul: the same contract as the tensor-core kernels (fp32 accumulation,
+// round-to-nearest-even output) for shapes and pointers that TMA cannot address (row pitch or base not
+// 16-byte aligned, K == 0) and for operands with arbitrary row and column strides. Any M, N, K and any alignment.
 // 64 x 64 output tile per CTA, 16-deep k-slices through shared memory, 4 x 4 outputs per thread.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -36,7 +36,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(int M, int N, int K, con
                                                         const typename Elem<DT>::T *__restrict__ B, long long ldb,
                                                         long long strideB, typename Elem<DT>::T *__restrict__ C,
                                                         long long ldc, long long strideC,
-                                                        const typename Elem<DT>::T *__restrict__ bias, int act)
+                                                        const typename Elem<DT>::T *__restrict__ bias, int act, long long a_cs,
+                                                        long long b_cs)
 {
     constexpr int TM = 64, TN = 64, TK = 16;
     __shared__ float As[TK][TM + 1];
@@ -52,12 +53,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(int M, int N, int K, con
         for (int i = threadIdx.x; i < TM * TK; i += 256) {
             const int r = i / TK, c = i % TK;
             const int gm = m0 + r, gk = k0 + c;
-            As[c][r] = (gm < M && gk < K) ? Elem<DT>::load(A + (long long)gm * lda + gk) : 0.0f;
+            As[c][r] = (gm < M && gk < K) ? Elem<DT>::load(A + (long long)gm * lda + (long long)gk * a_cs) : 0.0f;
         }
         for (int i = threadIdx.x; i < TK * TN; i += 256) {
             const int r = i / TN, c = i % TN;
             const int gk = k0 + r, gn = n0 + c;
-            Bs[r][c] = (gk < K && gn < N) ? Elem<DT>::load(B + (long long)gk * ldb + gn) : 0.0f;
+            Bs[r][c] = (gk < K && gn < N) ? Elem<DT>::load(B + (long long)gk * ldb + (long long)gn * b_cs) : 0.0f;
         }
         __syncthreads();
 #pragma unroll
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(int M, int N, int K, con
 
 int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K, const void *A, long long lda,
                      long long strideA, const void *B, long long ldb, long long strideB, void *C, long long ldc,
-                     long long strideC, const void *bias, int act)
+                     long long strideC, const void *bias, int act, long long a_cs, long long b_cs)
 {
     if (M == 0 || N == 0 || batch == 0) return BTM_OK;
     const long long gy = (M + 63) / 64, gx = (N + 63) / 64;
@@ -102,15 +103,15 @@ int launch_gemm_simt(int dtype, cudaStream_t st, int batch, int M, int N, int K,
     switch (dtype) {
     case BTM_F32:
         gemm_simt_kernel<BTM_F32><<<grid, 256, 0, st>>>(M, N, K, (const float *)A, lda, strideA, (const float *)B, ldb, strideB,
-                                                        (float *)C, ldc, strideC, (const float *)bias, act);
+                                                        (float *)C, ldc, strideC, (const float *)bias, act, a_cs, b_cs);
         break;
     case BTM_F16:
         gemm_simt_kernel<BTM_F16><<<grid, 256, 0, st>>>(M, N, K, (const __half *)A, lda, strideA, (const __half *)B, ldb, strideB,
-                                                        (__half *)C, ldc, strideC, (const __half *)bias, act);
+                                                        (__half *)C, ldc, strideC, (const __half *)bias, act, a_cs, b_cs);
         break;
     case BTM_BF16:
         gemm_simt_kernel<BTM_BF16><<<grid, 256, 0, st>>>(M, N, K, (const __nv_bfloat16 *)A, lda, strideA, (const __nv_bfloat16 *)B,
-                                                         ldb, strideB, (__nv_bfloat16 *)C, ldc, strideC, (const __nv_bfloat16 *)bias, act);
+                                                         ldb, strideB, (__nv_bfloat16 *)C, ldc, strideC, (const __nv_bfloat16 *)bias, act, a_cs, b_cs);
         break;
     default:
         return set_error(BTM_ERR_UNSUPPORTED, "matmul: dtype %d is not supported", dtype);

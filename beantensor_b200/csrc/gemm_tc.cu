@@ -27,8 +27,11 @@ constexpr int BM = 128;          // rows of one output tile = accumulator lanes
 constexpr int SLICE_BYTES = 128; // bytes of K (for A) or N (for B) per shared-memory row = swizzle span
 constexpr int UMMA_K_BYTES = 32; // bytes of K consumed by one tcgen05.mma
 constexpr int NUM_THREADS = 192;
+#ifndef BTM_TC1_KPS
+#define BTM_TC1_KPS 1
+#endif
 
-template <int BN, int DT, bool BT = false>
+template <int BN, int DT, bool BT = false, bool AT = false>
 struct TileCfg {
     static constexpr bool kTf32 = (DT == BTM_F32);
     static constexpr int kEs = kTf32 ? 4 : 2;              // element bytes
@@ -38,13 +41,21 @@ struct TileCfg {
     // kBKE rows x 128 B. The fp32 planes are written transposed ([N,K]) by the split pass, so B
     // is K-major like A: BN rows x 128 B from a single TMA box.
     static constexpr bool kBMnMajor = !kTf32 && !BT; // BT: the caller's B is already [N,K] (K-major)
+    // AT: the caller's A is stored [K,M] (M contiguous): it is loaded as M-contiguous 128-byte chunks (BM/64 of them,
+    // 64 k-rows x 128 B each) and consumed as an MN-major operand, exactly as B is when it is row-major [K,N].
+    static constexpr bool kAMnMajor = !kTf32 && AT;
+    static constexpr int kAChunks = BM / (SLICE_BYTES / kEs);
     static constexpr int kChunkN = SLICE_BYTES / kEs;       // n elements per MN-major B chunk
     static constexpr int kChunks = BN / kChunkN;            // MN-major B chunks per stage
     static constexpr int kChunkBytes = kBKE * SLICE_BYTES;  // one MN-major chunk: kBKE rows of 128 B
     static constexpr int kABytes = BM * SLICE_BYTES;        // one A plane
     static constexpr int kBBytes = BN * SLICE_BYTES;        // one B plane (either major)
-    static constexpr int kStageBytes = kPlanes * (kABytes + kBBytes);
-    static constexpr int kStages = (kStageBytes <= 48 * 1024) ? 4 : 3;
+    static constexpr int kKbBytes = kPlanes * (kABytes + kBBytes); // one k-block of operands
+    // k-blocks per pipeline stage (16-bit kernels; the fp32 planes leave no room): one barrier round trip and one
+    // commit per kKps k-blocks, as in the two-SM kernel.
+    static constexpr int kKps = kTf32 ? 1 : BTM_TC1_KPS;
+    static constexpr int kStageBytes = kKps * kKbBytes;
+    static constexpr int kStages = (kKbBytes <= 48 * 1024 ? 4 : 3) / kKps;
     static constexpr int kSmemBytes = kStages * kStageBytes + EPI_SMEM_BYTES + 1024; // ring + epilogue staging + alignment slack
     static constexpr int kTmemCols = 2 * BN;                // two accumulators
     static constexpr int kKSteps = SLICE_BYTES / UMMA_K_BYTES;
@@ -82,12 +93,12 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int tile_i
     return c;
 }
 
-template <int BN, int DT, bool BT = false>
+template <int BN, int DT, bool BT = false, bool AT = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ StoreMaps cmaps, const GemmParams p)
 {
-    using Cfg = TileCfg<BN, DT, BT>;
+    using Cfg = TileCfg<BN, DT, BT, AT>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[Cfg::kStages];
     __shared__ __align__(8) uint64_t bar_empty[Cfg::kStages];
@@ -132,28 +143,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const TileCoord tc = decode_tile<BN>(p, tile);
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = 0; kb < p.num_kb; kb += Cfg::kKps) {
                     if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY, p.wait_limit)) {
                         ok = false;
                         break;
                     }
+                    const int nsub = min(Cfg::kKps, p.num_kb - kb); // the last stage of a tile may be short
                     const uint32_t full = smem_u32(&bar_full[stage]);
-                    const uint32_t sbase = smem_base + stage * Cfg::kStageBytes;
                     // A tail tile (16-bit only) loads half of the B chunks.
                     const int chunks = Cfg::kBMnMajor ? tc.bn / Cfg::kChunkN : 0;
-                    mbar_expect_tx(full, Cfg::kBMnMajor ? (uint32_t)(Cfg::kABytes + chunks * Cfg::kChunkBytes) : (uint32_t)Cfg::kStageBytes);
-                    const int k0 = kb * Cfg::kBKE;
+                    mbar_expect_tx(full, (uint32_t)nsub * (Cfg::kBMnMajor ? (uint32_t)(Cfg::kABytes + chunks * Cfg::kChunkBytes) : (uint32_t)Cfg::kKbBytes));
+                    for (int sub = 0; sub < nsub; ++sub) {
+                        const uint32_t sbase = smem_base + stage * Cfg::kStageBytes + sub * Cfg::kKbBytes;
+                        const int k0 = (kb + sub) * Cfg::kBKE;
 #pragma unroll
-                    for (int pl = 0; pl < Cfg::kPlanes; ++pl) {
-                        const int z = Cfg::kTf32 ? pl : tc.b;
-                        tma_load_3d(sbase + pl * Cfg::kABytes, &tmA, k0, tc.m * BM, z, full);
-                        const uint32_t bbase = sbase + Cfg::kPlanes * Cfg::kABytes + pl * Cfg::kBBytes;
-                        if constexpr (Cfg::kBMnMajor) {
+                        for (int pl = 0; pl < Cfg::kPlanes; ++pl) {
+                            const int z = Cfg::kTf32 ? pl : tc.b;
+                            if constexpr (Cfg::kAMnMajor) {
 #pragma unroll
-                            for (int c = 0; c < Cfg::kChunks; ++c)
-                                if (c < chunks) tma_load_3d(bbase + c * Cfg::kChunkBytes, &tmB, tc.n0 + c * Cfg::kChunkN, k0, z, full);
-                        } else {
-                            tma_load_3d(bbase, &tmB, k0, tc.n0, z, full);
+                                for (int c = 0; c < Cfg::kAChunks; ++c)
+                                    tma_load_3d(sbase + c * Cfg::kChunkBytes, &tmA, tc.m * BM + c * Cfg::kChunkN, k0, z, full);
+                            } else {
+                                tma_load_3d(sbase + pl * Cfg::kABytes, &tmA, k0, tc.m * BM, z, full);
+                            }
+                            const uint32_t bbase = sbase + Cfg::kPlanes * Cfg::kABytes + pl * Cfg::kBBytes;
+                            if constexpr (Cfg::kBMnMajor) {
+#pragma unroll
+                                for (int c = 0; c < Cfg::kChunks; ++c)
+                                    if (c < chunks) tma_load_3d(bbase + c * Cfg::kChunkBytes, &tmB, tc.n0 + c * Cfg::kChunkN, k0, z, full);
+                            } else {
+                                tma_load_3d(bbase, &tmB, k0, tc.n0, z, full);
+                            }
                         }
                     }
                     if (++stage == Cfg::kStages) {
@@ -167,8 +187,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t kFmt = Cfg::kTf32 ? 2u : (DT == BTM_BF16 ? 1u : 0u);
-            constexpr uint32_t idesc_full = make_idesc(kFmt, false, Cfg::kBMnMajor, BM, BN);
-            constexpr uint32_t idesc_half = make_idesc(kFmt, false, Cfg::kBMnMajor, BM, BN / 2);
+            constexpr uint32_t idesc_full = make_idesc(kFmt, Cfg::kAMnMajor, Cfg::kBMnMajor, BM, BN);
+            constexpr uint32_t idesc_half = make_idesc(kFmt, Cfg::kAMnMajor, Cfg::kBMnMajor, BM, BN / 2);
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
@@ -180,32 +200,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag, p.status, WAIT_MMA_TMEM_EMPTY, p.wait_limit)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = 0; kb < p.num_kb; kb += Cfg::kKps) {
                     if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.status, WAIT_MMA_FULL, p.wait_limit)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sbase = smem_base + stage * Cfg::kStageBytes;
-                    const uint32_t a0 = sbase, b0 = sbase + Cfg::kPlanes * Cfg::kABytes;
+                    const int nsub = min(Cfg::kKps, p.num_kb - kb);
+                    for (int sub = 0; sub < nsub; ++sub) {
+                        const uint32_t sbase = smem_base + stage * Cfg::kStageBytes + sub * Cfg::kKbBytes;
+                        const uint32_t a0 = sbase, b0 = sbase + Cfg::kPlanes * Cfg::kABytes;
 #pragma unroll
-                    for (int ks = 0; ks < Cfg::kKSteps; ++ks) {
-                        // A: K-major, 8-row groups 1024 B apart; a k-step moves 32 B inside the swizzle span.
-                        // B: MN-major, n-chunks kChunkBytes apart (leading offset), 8-k-row groups 1024 B
-                        // apart (stride offset); a k-step moves kUmmaKRows rows of 128 B.
-                        const uint64_t a_hi = make_smem_desc_sw128(a0 + ks * UMMA_K_BYTES, 16, 1024);
-                        const uint64_t b_hi = Cfg::kBMnMajor
-                                                  ? make_smem_desc_sw128(b0 + ks * Cfg::kUmmaKRows * SLICE_BYTES, Cfg::kChunkBytes, 1024)
-                                                  : make_smem_desc_sw128(b0 + ks * UMMA_K_BYTES, 16, 1024);
-                        const uint32_t first = (kb | ks) != 0;
-                        if constexpr (Cfg::kTf32) {
-                            const uint64_t a_lo = make_smem_desc_sw128(a0 + Cfg::kABytes + ks * UMMA_K_BYTES, 16, 1024);
-                            const uint64_t b_lo = make_smem_desc_sw128(b0 + Cfg::kBBytes + ks * UMMA_K_BYTES, 16, 1024);
-                            umma<1, true>(d_tmem, a_lo, b_hi, idesc, first);
-                            umma<1, true>(d_tmem, a_hi, b_lo, idesc, 1u);
-                            umma<1, true>(d_tmem, a_hi, b_hi, idesc, 1u);
-                        } else {
-                            umma<1, false>(d_tmem, a_hi, b_hi, idesc, first);
+                        for (int ks = 0; ks < Cfg::kKSteps; ++ks) {
+                            // A: K-major, 8-row groups 1024 B apart; a k-step moves 32 B inside the swizzle span.
+                            // B: MN-major, n-chunks kChunkBytes apart (leading offset), 8-k-row groups 1024 B
+                            // apart (stride offset); a k-step moves kUmmaKRows rows of 128 B.
+                            const uint64_t a_hi = Cfg::kAMnMajor
+                                                      ? make_smem_desc_sw128(a0 + ks * Cfg::kUmmaKRows * SLICE_BYTES, Cfg::kChunkBytes, 1024)
+                                                      : make_smem_desc_sw128(a0 + ks * UMMA_K_BYTES, 16, 1024);
+                            const uint64_t b_hi = Cfg::kBMnMajor
+                                                      ? make_smem_desc_sw128(b0 + ks * Cfg::kUmmaKRows * SLICE_BYTES, Cfg::kChunkBytes, 1024)
+                                                      : make_smem_desc_sw128(b0 + ks * UMMA_K_BYTES, 16, 1024);
+                            const uint32_t first = (kb | sub | ks) != 0;
+                            if constexpr (Cfg::kTf32) {
+                                const uint64_t a_lo = make_smem_desc_sw128(a0 + Cfg::kABytes + ks * UMMA_K_BYTES, 16, 1024);
+                                const uint64_t b_lo = make_smem_desc_sw128(b0 + Cfg::kBBytes + ks * UMMA_K_BYTES, 16, 1024);
+                                umma<1, true>(d_tmem, a_lo, b_hi, idesc, first);
+                                umma<1, true>(d_tmem, a_hi, b_lo, idesc, 1u);
+                                umma<1, true>(d_tmem, a_hi, b_hi, idesc, 1u);
+                            } else {
+                                umma<1, false>(d_tmem, a_hi, b_hi, idesc, first);
+                            }
                         }
                     }
                     umma_commit(smem_u32(&bar_empty[stage])); // stage reusable once these MMAs have read it
@@ -372,10 +397,10 @@ int launch_split_tf32(cudaStream_t st, const float *src, long long ld, int rows,
     return check_cuda(cudaGetLastError(), "split_tf32 launch");
 }
 
-template <int BN, int DT, bool BT = false>
+template <int BN, int DT, bool BT = false, bool AT = false>
 static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm, GemmParams p)
 {
-    using Cfg = TileCfg<BN, DT, BT>;
+    using Cfg = TileCfg<BN, DT, BT, AT>;
     p.tiles_m = (p.M + BM - 1) / BM;
     p.tiles_n = (p.N + BN - 1) / BN;
     p.num_kb = (p.K + Cfg::kBKE - 1) / Cfg::kBKE;
@@ -392,15 +417,15 @@ static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, con
     p.tiles_tail = 2 * tail_big;
     const long long sched = (long long)p.tiles_full + p.tiles_tail;
     const int grid = (int)(sched < sm_count ? sched : sm_count);
-    gemm_tc_kernel<BN, DT, BT><<<grid, NUM_THREADS, Cfg::kSmemBytes, st>>>(tmA, tmB, cm, p);
+    gemm_tc_kernel<BN, DT, BT, AT><<<grid, NUM_THREADS, Cfg::kSmemBytes, st>>>(tmA, tmB, cm, p);
     return check_cuda(cudaGetLastError(), "gemm_tc launch");
 }
 
-template <int BN, int DT, bool BT = false>
+template <int BN, int DT, bool BT = false, bool AT = false>
 static cudaError_t raise_smem()
 {
-    return cudaFuncSetAttribute(gemm_tc_kernel<BN, DT, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                TileCfg<BN, DT, BT>::kSmemBytes);
+    return cudaFuncSetAttribute(gemm_tc_kernel<BN, DT, BT, AT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                TileCfg<BN, DT, BT, AT>::kSmemBytes);
 }
 
 int configure_gemm_tc_kernels()
@@ -416,6 +441,14 @@ int configure_gemm_tc_kernels()
     if (e == cudaSuccess) e = raise_smem<256, BTM_BF16, true>();
     if (e == cudaSuccess) e = raise_smem<128, BTM_F16, true>();
     if (e == cudaSuccess) e = raise_smem<128, BTM_BF16, true>();
+    if (e == cudaSuccess) e = raise_smem<256, BTM_F16, false, true>();
+    if (e == cudaSuccess) e = raise_smem<256, BTM_BF16, false, true>();
+    if (e == cudaSuccess) e = raise_smem<128, BTM_F16, false, true>();
+    if (e == cudaSuccess) e = raise_smem<128, BTM_BF16, false, true>();
+    if (e == cudaSuccess) e = raise_smem<256, BTM_F16, true, true>();
+    if (e == cudaSuccess) e = raise_smem<256, BTM_BF16, true, true>();
+    if (e == cudaSuccess) e = raise_smem<128, BTM_F16, true, true>();
+    if (e == cudaSuccess) e = raise_smem<128, BTM_BF16, true, true>();
     return check_cuda(e, "cudaFuncSetAttribute(gemm_tc)");
 }
 
@@ -444,6 +477,27 @@ int launch_gemm_tc(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &
     }
     if (bn == 128) return launch_one<128, BTM_BF16>(st, sm_count, tmA, tmB, cm, p);
     return launch_one<256, BTM_BF16>(st, sm_count, tmA, tmB, cm, p);
+}
+
+// 16-bit product with operands in either storage order: a_t: A is stored [K,M] (tensor map dims (M, K), box 64 x 64);
+// b_t: B is stored [N,K] (K-major; tensor map dims (K, N), box 64 x bn, so the caller fixes bn = 256 or 128).
+int launch_gemm_tc_layout(int dtype, cudaStream_t st, int sm_count, const CUtensorMap &tmA, const CUtensorMap &tmB, const StoreMaps &cm,
+                          const GemmParams &p, int bn, bool a_t, bool b_t)
+{
+#define BTM_LAYOUT_CASE(BTV, ATV)                                                                      \
+    do {                                                                                               \
+        if (dtype == BTM_F16) {                                                                        \
+            if (bn == 128) return launch_one<128, BTM_F16, BTV, ATV>(st, sm_count, tmA, tmB, cm, p);   \
+            return launch_one<256, BTM_F16, BTV, ATV>(st, sm_count, tmA, tmB, cm, p);                  \
+        }                                                                                              \
+        if (bn == 128) return launch_one<128, BTM_BF16, BTV, ATV>(st, sm_count, tmA, tmB, cm, p);      \
+        return launch_one<256, BTM_BF16, BTV, ATV>(st, sm_count, tmA, tmB, cm, p);                     \
+    } while (0)
+    if (a_t && b_t) BTM_LAYOUT_CASE(true, true);
+    if (a_t) BTM_LAYOUT_CASE(false, true);
+    if (b_t) BTM_LAYOUT_CASE(true, false);
+    BTM_LAYOUT_CASE(false, false);
+#undef BTM_LAYOUT_CASE
 }
 
 // 16-bit product with B given transposed ([N,K] row-major, i.e. K-major): C = A . Bt^T. The B box of

@@ -84,21 +84,28 @@ inline void matmul_bias_act_gpu(const btm_tensor_view &a, const btm_tensor_view 
                                 relu ? BTM_ACT_RELU : BTM_ACT_NONE, const_cast<void *>(btm_base(out)), ldc));
 }
 
-// out[M,N] = a[M,K] . b[K,N]. Float16/BFloat16 (fp32 accumulate) or Float32 (3xTF32).
+// Operands may be any 2-D view (Tensor::strides, Tensor/Tensor.h:173-195): row-major, transposed or strided.
+inline void btm_require_gpu_2d(const btm_tensor_view &t, const char *name)
+{
+    if (t.device != 1) throw std::invalid_argument(std::string(name) + ": Tensor is not on the GPU"); // guard of TensorOps.cu:89-93
+    if (t.ndim != 2) throw std::invalid_argument(std::string(name) + ": wrong rank");
+}
+
+// out[M,N] = a[M,K] . b[K,N]. Float16/BFloat16 (fp32 accumulate) or Float32 (3xTF32). a and b may be transposed or
+// strided views (no copy is made); out is row-major.
 inline void matmul_gpu(const btm_tensor_view &a, const btm_tensor_view &b, btm_tensor_view &out, void *stream = nullptr)
 {
-    btm_require_gpu_rowmajor(a, 2, "matmul_gpu(a)");
-    btm_require_gpu_rowmajor(b, 2, "matmul_gpu(b)");
+    btm_require_gpu_2d(a, "matmul_gpu(a)");
+    btm_require_gpu_2d(b, "matmul_gpu(b)");
     btm_require_gpu_rowmajor(out, 2, "matmul_gpu(out)");
     if (a.dtype != b.dtype || a.dtype != out.dtype) throw std::invalid_argument("matmul_gpu: dtypes differ");
     if (a.gpu_id != b.gpu_id || a.gpu_id != out.gpu_id) throw std::invalid_argument("matmul_gpu: tensors live on different GPUs");
     if (a.shape[1] != b.shape[0] || out.shape[0] != a.shape[0] || out.shape[1] != b.shape[1])
         throw std::invalid_argument("matmul_gpu: shape mismatch");
     const int M = (int)a.shape[0], K = (int)a.shape[1], N = (int)b.shape[1];
-    const int64_t lda = M > 1 ? (int64_t)a.strides[0] : (K > 0 ? K : 1);
-    const int64_t ldb = K > 1 ? (int64_t)b.strides[0] : (N > 0 ? N : 1);
     const int64_t ldc = M > 1 ? (int64_t)out.strides[0] : (N > 0 ? N : 1);
-    btm_raise(btm_gemm(a.gpu_id, stream, a.dtype, M, N, K, btm_base(a), lda, btm_base(b), ldb, const_cast<void *>(btm_base(out)), ldc));
+    btm_raise(btm_gemm_strided(a.gpu_id, stream, a.dtype, M, N, K, btm_base(a), (int64_t)a.strides[0], (int64_t)a.strides[1], btm_base(b),
+                               (int64_t)b.strides[0], (int64_t)b.strides[1], const_cast<void *>(btm_base(out)), ldc));
 }
 
 // out[b] = a[b] . b[b]; dense row-major matrices with a batch stride.

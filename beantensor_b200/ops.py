@@ -78,11 +78,20 @@ def matmul_gpu(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bias: torch.
     K2, N = b.shape
     if K != K2 or out.shape != (M, N):
         raise ValueError(f"matmul_gpu: shape mismatch {tuple(a.shape)} x {tuple(b.shape)} -> {tuple(out.shape)}")
-    for t, n in ((a, "a"), (b, "b"), (out, "out")):
-        _rowmajor(t, n)
+    _rowmajor(out, "out")
+    ldc = out.stride(0) if M > 1 else max(N, 1)
+    a_row = a.stride(1) == 1 or K <= 1
+    b_row = b.stride(1) == 1 or N <= 1
+    if not (a_row and b_row):
+        # Transposed or strided views (Tensor::strides, Tensor/Tensor.h:173-195) go through without a copy.
+        if bias is not None or relu:
+            raise ValueError("matmul_gpu: the fused epilogue takes row-major operands")
+        rc = _LIB().btm_gemm_strided(dev, _stream(dev), _DT[a.dtype], M, N, K, a.data_ptr(), a.stride(0), a.stride(1),
+                                     b.data_ptr(), b.stride(0), b.stride(1), out.data_ptr(), ldc)
+        raise_for_status(rc)
+        return
     lda = a.stride(0) if M > 1 else max(K, 1)
     ldb = b.stride(0) if K > 1 else max(N, 1)
-    ldc = out.stride(0) if M > 1 else max(N, 1)
     if bias is None and not relu:
         rc = _lib.lib().btm_gemm(dev, _stream(dev), _DT[a.dtype], M, N, K, a.data_ptr(), lda, b.data_ptr(), ldb,
                                  out.data_ptr(), ldc)

@@ -145,6 +145,17 @@ int btm_gemm_bias_act(int device, void *stream, int dtype, int M, int N, int K, 
 int btm_gemm_bt(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t lda, const void *Bt,
                 int64_t ldbt, void *C, int64_t ldc);
 
+/* The same product for operands that are not row-major: A[m,k] lies at A + m*a_rs + k*a_cs and B[k,n] at
+ * B + k*b_rs + n*b_cs (element strides, as in Tensor::strides, Tensor/Tensor.h:173-195); C stays row-major with ldc.
+ * This is what lets matmul(transpose(a), b), matmul(a, transpose(b)) and products of strided views run without a copy;
+ * the reference's Ops/Algebra/Transpose is an empty stub (Ops/Algebra/Transpose/Transpose.h), so its callers would
+ * have to materialise such operands first. An operand with unit stride along either index takes the tensor-core
+ * kernels (a transposed 16-bit operand is read as an MN-major tensor-core operand through its tensor map; the fp32
+ * split pass reads its operands in whatever order they are stored), provided bases and pitches are multiples of
+ * 16 bytes; anything else takes the general CUDA-core kernel with the same arithmetic contract. Strides >= 0. */
+int btm_gemm_strided(int device, void *stream, int dtype, int M, int N, int K, const void *A, int64_t a_rs, int64_t a_cs,
+                     const void *B, int64_t b_rs, int64_t b_cs, void *C, int64_t ldc);
+
 /* Same product for BTM_F32 with caller-owned scratch instead of the library's:
  * `workspace` is device memory of at least btm_gemm_f32_workspace_bytes(M,N,K) bytes,
  * 256-byte aligned. Nothing is allocated. */

@@ -315,3 +315,32 @@ def test_user_level_matmul_and_views_with_an_offset(btm, oracle, dtype):
         out3 = btm.matmul(to_gpu(A3, dtype), to_gpu(B3, dtype))
         assert out3.shape == (2, M, N)
         assert oracle.rel_frobenius(to_host_bits(out3, dtype), dtype, oracle.bmm(dtype, A3, B3)) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [_lib.F16, _lib.BF16, _lib.F32])
+@pytest.mark.parametrize("layout", ["at", "bt", "at_bt", "strided", "at_unaligned"])
+def test_transposed_and_strided_operands_without_a_copy(btm, oracle, dtype, layout):
+    # matmul(transpose(a), b), matmul(a, transpose(b)), both, and views with arbitrary strides: Tensor::strides are
+    # honoured (Tensor/Tensor.h:173-195) instead of asking the caller to materialise the operand.
+    import torch
+    shapes = [(256, 384, 192), (300, 200, 130), (128, 136, 72)] if layout != "at_unaligned" else [(131, 77, 53)]
+    for (M, N, K) in shapes:
+        A, B = gemm_inputs(dtype, M, N, K, 61 + M, "uniform" if dtype == _lib.F32 else "normal")
+        a, b = to_gpu(A, dtype), to_gpu(B, dtype)
+        if layout in ("at", "at_bt", "at_unaligned"):
+            a = a.t().contiguous().t()          # stored [K, M]: unit stride along m
+            assert a.stride(0) == 1
+        if layout in ("bt", "at_bt"):
+            b = b.t().contiguous().t()          # stored [N, K]: unit stride along k
+            assert b.stride(1) == K and b.stride(0) == 1
+        if layout == "strided":
+            big_a = torch.zeros((2 * M, 3 * K), dtype=torch_dtype(dtype), device="cuda")
+            big_b = torch.zeros((2 * K, 2 * N), dtype=torch_dtype(dtype), device="cuda")
+            big_a[::2, ::3] = a
+            big_b[::2, ::2] = b
+            a, b = big_a[::2, ::3], big_b[::2, ::2]
+        out = torch.full((M, N), float("nan"), dtype=torch_dtype(dtype), device="cuda")
+        btm.matmul_gpu(a, b, out)
+        btm.check_device_status(0)
+        err = oracle.rel_frobenius(to_host_bits(out, dtype), dtype, oracle.gemm(dtype, A, B))
+        assert err <= TOL[dtype], (layout, (M, N, K), err)
