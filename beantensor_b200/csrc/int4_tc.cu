@@ -166,7 +166,22 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     constexpr int SC_PRE = 6; // per-thread prefetch depth; the rest (long K or small groups) is fetched afterwards
     __half sc_pre[SC_PRE];
     const int sc_total = BW * g_cnt, G = p.K / group;
-    if (warp >= 3) {
+#ifndef BTM_I4TC_SCALES_DIRECT
+#define BTM_I4TC_SCALES_DIRECT 0
+#endif
+    // Direct form: a dequantising thread (= weight row) fetches the two scales of a unit from global memory one unit
+    // ahead of their use, so nothing is staged and the eight warps do not meet before their first unit.
+    __half sd0 = __ushort_as_half((unsigned short)0), sd1 = sd0;
+    if (BTM_I4TC_SCALES_DIRECT && warp >= 3 && n_units > 0) {
+        const int grp0 = (warp - 3) >> 2, row0 = (warp & 3) * 32 + lane;
+        if (grp0 < n_units) {
+            const int u = unit_at(grp0);
+            const __half *grow = scales + (size_t)min(n0 + row0, p.N - 1) * G;
+            sd0 = __ldg(grow + (u * UNIT_K) / group);
+            sd1 = __ldg(grow + (u * UNIT_K + BKE) / group);
+        }
+    }
+    if (!BTM_I4TC_SCALES_DIRECT && warp >= 3) {
 #pragma unroll
         for (int j = 0; j < SC_PRE; ++j) {
             const int i = (int)threadIdx.x - DQ_FIRST + j * 256;
@@ -279,17 +294,20 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         const int dq = threadIdx.x - DQ_FIRST; // 0..255
         const int grp = (warp - 3) >> 2, row = (warp & 3) * 32 + lane;
         // The prefetched scales go to shared memory; the eight warps meet on a named barrier of their own.
+        if (!BTM_I4TC_SCALES_DIRECT) {
 #pragma unroll
-        for (int j = 0; j < SC_PRE; ++j) {
-            const int i = dq + j * 256;
-            if (i < sc_total) sc_s[i] = sc_pre[j];
+            for (int j = 0; j < SC_PRE; ++j) {
+                const int i = dq + j * 256;
+                if (i < sc_total) sc_s[i] = sc_pre[j];
+            }
+            for (int i = dq + SC_PRE * 256; i < sc_total; i += 256) {
+                const int r = i / g_cnt, g = i - r * g_cnt;
+                sc_s[i] = __ldg(scales + (size_t)min(n0 + r, p.N - 1) * G + g_first + g);
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
         }
-        for (int i = dq + SC_PRE * 256; i < sc_total; i += 256) {
-            const int r = i / g_cnt, g = i - r * g_cnt;
-            sc_s[i] = __ldg(scales + (size_t)min(n0 + r, p.N - 1) * G + g_first + g);
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
         const __half *srow = sc_s + row * g_cnt - g_first;
+        const __half *grow = scales + (size_t)min(n0 + row, p.N - 1) * G;
         const uint32_t xs = (uint32_t)((row >> 1) & 3);
         const uint32_t raw_row0 = raw_ring + (uint32_t)row * 64u;
         const uint32_t tmem_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)MB;
@@ -305,7 +323,19 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                              : "=r"(pw[c].x), "=r"(pw[c].y), "=r"(pw[c].z), "=r"(pw[c].w)
                              : "r"(raw_row0 + rs * RAW_BYTES + ((((uint32_t)c) ^ xs) << 4)));
-            const __half2 s0 = __half2half2(srow[(u * UNIT_K) / group]), s1 = __half2half2(srow[(u * UNIT_K + BKE) / group]);
+            __half2 s0, s1;
+            if (BTM_I4TC_SCALES_DIRECT) {
+                s0 = __half2half2(sd0);
+                s1 = __half2half2(sd1);
+                if (i + 2 < n_units) { // the scales of this warp group's next unit, in flight while this one is unpacked
+                    const int un = unit_at(i + 2);
+                    sd0 = __ldg(grow + (un * UNIT_K) / group);
+                    sd1 = __ldg(grow + (un * UNIT_K + BKE) / group);
+                }
+            } else {
+                s0 = __half2half2(srow[(u * UNIT_K) / group]);
+                s1 = __half2half2(srow[(u * UNIT_K + BKE) / group]);
+            }
             uint4 d[8];
             d[0] = dequant_word(pw[0].x, s0);
             d[1] = dequant_word(pw[0].y, s0);

@@ -831,6 +831,29 @@ def run_multi(args, peaks):
     got_block = hc.view(torch.uint16)
     e2e_ok = bool(torch.equal(got_block, c_dev[:, c_lo:c_hi].cpu().view(torch.uint16)))
 
+    # ---- two sharded products in a row, whole against pipelined by row panels (GEMM -> all-gather -> next GEMM)
+    from beantensor_b200.pipeline import TwoLayerNShard
+    b2_block = synth_f16((n, nloc), n ** -0.5, 4, 100 + rank, dtype).cuda()
+    c2 = torch.empty((n, nloc), dtype=dtype, device="cuda")
+    # panels: as many as still leave each panel of layer 1 about two waves of 256 x 256 tiles on 74 CTA pairs
+    panels = 2
+    while panels * 2 <= 16 and (n // (panels * 2) // 256) * (nloc // 256) >= 148:
+        panels *= 2
+    chain = TwoLayerNShard(dist, local_rank, rank, world, _lib.BF16, a, b_block, b2_block,
+                           mcb.local_ptr if mcb is not None else None, mcb.mc_ptr if mcb is not None else None,
+                           None if mcb is not None else c_buf.peers, c_dev, c2, panels=panels)
+    seq_ms, _, _ = time_reps(torch, dist, world, lambda i: chain.run_sequential(), 3, 2, 0.1, 10)
+    c2_seq = c2.clone()
+    pipe_ms, _, _ = time_reps(torch, dist, world, lambda i: chain.run_pipelined(), 3, 2, 0.1, 10)
+    ops.check_device_status(local_rank)
+    two_layer = {"what": "C2[:, block] = (A . B1) . B2[:, block]: layer 1 N-sharded with fused all-gather, layer 2 on the gathered C1; "
+                         f"two whole products with a barrier between them against {panels} row panels on three streams",
+                 "sequential_ms": statistics.median(seq_ms) / 3, "pipelined_ms": statistics.median(pipe_ms) / 3,
+                 "speedup": statistics.median(seq_ms) / statistics.median(pipe_ms),
+                 "results_equal_bitwise": bool(torch.equal(c2.view(torch.int16), c2_seq.view(torch.int16)))}
+    del b2_block, c2, c2_seq, chain
+    torch.cuda.empty_cache()
+
     # ---- batch-sharded batched matmul (no collective)
     bmm_records = [bench_bmm_sharded(torch, dist, ops, rank, world, peaks, 200, weak=False),
                    bench_bmm_sharded(torch, dist, ops, rank, world, peaks, 200, weak=True)]
@@ -857,6 +880,7 @@ def run_multi(args, peaks):
             "roofline": roof,
             "nccl_comparator": comparator,
             "peer_store_comparator": other,
+            "two_layer_pipeline": two_layer,
             "cpu_baseline": None,
             "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": panel_bytes + n * nloc * 2, "d2h_bytes_per_step": n * nloc * 2,
                     "steps": e2e_steps, "bytes_are": "per rank", "result_checked": e2e_ok,

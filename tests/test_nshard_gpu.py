@@ -226,3 +226,95 @@ def test_multicast_entry_refuses_what_it_cannot_store(btm):
     assert L.btm_gemm_nshard_mc(0, None, _lib.F16, 8, 12, 64, p, 64, p, 12, p, p, 24, 0, 2) == _lib.ERR_UNSUPPORTED
     assert L.btm_gemm_nshard_mc(0, None, _lib.F32, 8, 8, 64, p, 64, p, 8, p, p, 16, 0, 2) == _lib.ERR_UNSUPPORTED
     assert L.btm_gemm_nshard_mc(0, None, _lib.F16, 8, 8, 64, p, 64, p, 8, None, p, 16, 0, 2) == _lib.ERR_INVALID
+
+
+def _rank_main_two_layer(rank, world, port, q):
+    # GEMM -> all-gather -> next GEMM, whole and pipelined by row panels, over plain peer memory.
+    sys.path.insert(0, ROOT)
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+    import torch
+    import torch.distributed as dist
+    from beantensor_b200 import ops
+    from beantensor_b200.errors import raise_for_status
+    from beantensor_b200.pipeline import TwoLayerNShard
+    from oracle import oracle as O
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ops.init(rank)
+        L = _lib.lib()
+        dtype = _lib.BF16
+        M, K1, N1, N2 = 512, 320, 256 * world, 128 * world
+        A, B1 = gemm_inputs(dtype, M, N1, K1, 71)
+        _, B2 = gemm_inputs(dtype, M, N2, N1, 72)
+        c0, c1 = sharding.column_block(N1, rank, world)
+        d0, d1 = sharding.column_block(N2, rank, world)
+        a = to_gpu(A, dtype)
+        b1 = to_gpu(np.ascontiguousarray(B1[:, c0:c1]), dtype)
+        b2 = to_gpu(np.ascontiguousarray(B2[:, d0:d1]), dtype)
+        ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+        raise_for_status(L.btm_ipc_alloc(rank, M * N1 * 2, C.byref(ptr), handle))
+        handles = [None] * world
+        dist.all_gather_object(handles, handle.raw)
+        peers = []
+        for r in range(world):
+            if r == rank:
+                peers.append(ptr.value)
+            else:
+                p = C.c_void_p()
+                raise_for_status(L.btm_ipc_open(rank, handles[r], C.byref(p)))
+                peers.append(p.value)
+
+        class Raw:
+            __cuda_array_interface__ = {"shape": (M, N1), "typestr": "<i2", "data": (ptr.value, False), "version": 2}
+
+        c1_view = torch.as_tensor(Raw(), device="cuda").view(torch.bfloat16)
+        c2 = torch.full((M, d1 - d0), float("nan"), dtype=torch.bfloat16, device="cuda")
+        chain = TwoLayerNShard(dist, rank, rank, world, dtype, a, b1, b2, None, None, peers, c1_view, c2, panels=4)
+        # what layer 2 multiplies is the ROUNDED C1, so the checker rounds it too
+        c1_ref = O.narrow(O.gemm(dtype, A, B1), dtype)
+        ref = O.gemm(dtype, c1_ref, np.ascontiguousarray(B2[:, d0:d1]))
+        errs = []
+        for run in (chain.run_sequential, chain.run_pipelined):
+            c1_view.fill_(float("nan"))
+            c2.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            run()
+            torch.cuda.synchronize()
+            dist.barrier()
+            ops.check_device_status(rank)
+            errs.append(float(O.rel_frobenius(c2.cpu().view(torch.uint16).numpy(), dtype, ref)))
+        for r in range(world):
+            if r != rank:
+                L.btm_ipc_close(rank, C.c_void_p(peers[r]))
+        dist.barrier()
+        L.btm_ipc_free(rank, ptr)
+        q.put((rank, errs))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_layer_chain_whole_and_pipelined(oracle):
+    import torch
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main_two_layer, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, errs in results:
+        for err in errs:
+            assert err <= 2 * TOL[_lib.BF16], (rank, errs)  # two roundings to bf16 on the way
