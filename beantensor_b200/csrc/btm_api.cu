@@ -38,12 +38,24 @@ int check_cuda(cudaError_t e, const char *what)
 // Test hooks (btm_debug_set): process-wide, read at every launch.
 static std::atomic<long long> g_dbg_wait_limit{0};
 static std::atomic<int> g_dbg_skip_loads{0};
+static std::atomic<int> g_dbg_bounds{-1};            // -1: not decided yet (BTM_DEBUG_BOUNDS is read once)
+static std::atomic<long long> g_dbg_bounds_shrink{0}; // test hook: pretend C is this many elements shorter
 
 void fill_wait_params(GemmParams *p)
 {
     const long long lim = g_dbg_wait_limit.load(std::memory_order_relaxed);
     p->wait_limit = lim > 0 ? lim : 2000000000LL; // about one second of SM clocks; the longest kernel here runs milliseconds
     p->debug_skip_loads = g_dbg_skip_loads.load(std::memory_order_relaxed);
+    int b = g_dbg_bounds.load(std::memory_order_relaxed);
+    if (b < 0) {
+        const char *e = getenv("BTM_DEBUG_BOUNDS");
+        b = (e && *e && strcmp(e, "0")) ? 1 : 0;
+        g_dbg_bounds.store(b);
+    }
+    p->debug_bounds = b;
+    const long long batches = p->batch > 1 ? p->batch : 1;
+    p->c_extent = (batches - 1) * p->strideC + (long long)(p->M > 0 ? p->M - 1 : 0) * p->ldc + p->col0 + p->N -
+                  g_dbg_bounds_shrink.load(std::memory_order_relaxed);
 }
 
 constexpr int kMaxDevices = 64;
@@ -352,6 +364,15 @@ int btm_debug_set(const char *key, long long value)
         g_dbg_skip_loads.store(value ? 1 : 0);
         return BTM_OK;
     }
+    if (!strcmp(key, "bounds")) {
+        g_dbg_bounds.store(value ? 1 : 0);
+        return BTM_OK;
+    }
+    if (!strcmp(key, "bounds_shrink")) {
+        if (value < 0) return set_error(BTM_ERR_INVALID, "debug switch bounds_shrink: negative value");
+        g_dbg_bounds_shrink.store(value);
+        return BTM_OK;
+    }
     return set_error(BTM_ERR_INVALID, "debug switch: unknown key '%s'", key);
 }
 
@@ -372,6 +393,8 @@ int btm_check_device_status(int device, void *stream)
     if (host != 0) {
         cudaMemsetAsync(ds->status, 0, sizeof(int), st);
         cudaStreamSynchronize(st);
+        if (host == 201)
+            return set_error(BTM_ERR_CUDA, "CUDA Error: a debug bounds check stopped a store outside the output (device status %d)", host);
         return set_error(BTM_ERR_TIMEOUT, "CUDA Error: a kernel wait ran out (device status %d)", host);
     }
     return BTM_OK;

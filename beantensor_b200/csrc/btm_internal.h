@@ -34,6 +34,12 @@ struct GemmParams {
     int *status;       // device status word (bounded waits report here)
     long long wait_limit; // SM cycles after which a wait inside the kernel gives up (set by fill_wait_params)
     int debug_skip_loads; // test hook: the producer warps issue no loads, so the consumers' waits run out
+    // Debug bounds checks (BTM_DEBUG_BOUNDS=1 or btm_debug_set("bounds", 1)): every address that an epilogue computes by
+    // hand from tile coordinates (the per-thread row stores, the peer stores and the multimem stores; TMA stores are
+    // clipped by the hardware) is compared with the extent of C before it is used. A store that would fall outside is
+    // skipped and code BOUNDS_STORE goes to the status word: the stand-in for a memory checker on this path.
+    int debug_bounds;
+    long long c_extent; // elements from a C base that this launch may touch: [0, c_extent)
 };
 
 // Output tensor maps of the epilogue's TMA stores, one per destination copy of C (local first, then peers).
@@ -50,7 +56,8 @@ struct DeviceState {
 };
 
 int set_error(int code, const char *fmt, ...);
-// Sets p->wait_limit (the default of about one second, or what btm_debug_set installed) and the test hook.
+// Sets p->wait_limit (the default of about one second, or what btm_debug_set installed), the test hooks and, from
+// the fields already set (M, N, batch, ldc, strideC, col0), the extent used by the debug bounds checks.
 void fill_wait_params(GemmParams *p);
 int check_cuda(cudaError_t e, const char *what);
 DeviceState *device_state(int device); // NULL + error set on failure
@@ -86,9 +93,9 @@ int configure_gemm_tc_kernels(); // raises dynamic shared-memory limits; once pe
 int configure_gemm_tc2_kernels();
 int configure_int4_tc_kernels();
 int configure_int4_gemv_kernels();
-int configure_int4_gemv_rows_kernels();
+int configure_int4_gemv_regs_kernels();
 // Register-resident GEMV. Returns a btm_status, or -1 when the shape is outside what it takes (nothing launched).
-int launch_int4_gemv_rows(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
+int launch_int4_gemv_regs(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
                           const void *scales, void *out);
 int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const void *act, const void *w, const void *scales, void *out,
                         int *status, int sm_count);

@@ -20,6 +20,7 @@ enum WaitCode : int {
     WAIT_EPI_TMEM_FULL = 104,
     WAIT_EPI_STAGE = 105,
     WAIT_PEER_CTA = 106,
+    BOUNDS_STORE = 201, // not a wait: a debug bounds check stopped a store
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -90,10 +90,21 @@ __device__ __forceinline__ void bias_act(const GemmParams &p, uint32_t (&v)[32],
     }
 }
 
+// Debug bounds check of a hand-computed store: elements [off, off + n) from a C base. False (and the code in the status
+// word) when the launch was started with bounds checks on and the range leaves the output; the caller skips the store.
+__device__ __forceinline__ bool store_in_bounds(const GemmParams &p, long long off, int n)
+{
+    if (!p.debug_bounds) return true;
+    if (off >= 0 && off + n <= p.c_extent) return true;
+    atomicCAS(p.status, 0, (int)BOUNDS_STORE);
+    return false;
+}
+
 // Per-thread stores of 32 consecutive columns of one output row (general path).
 template <int DT>
 __device__ __forceinline__ void store_row_direct(const GemmParams &p, const uint32_t (&acc)[32], long long elem_off, int ncols_valid)
 {
+    if (!store_in_bounds(p, elem_off, ncols_valid)) return;
     if constexpr (DT == BTM_F32) {
         for (int d = 0; d < p.ndst; ++d) {
             float *dst = reinterpret_cast<float *>(p.C[d]) + elem_off;
@@ -179,7 +190,8 @@ __device__ __forceinline__ void epilogue_band_multi(const GemmParams &p, const S
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const int row = row0 + 2 * i + (lane >> 4);
-                if (row < p.M && ccol + 8 <= p.N) multimem_st_v4(dst + base + (long long)row * p.ldc, regs[i]);
+                if (row < p.M && ccol + 8 <= p.N && store_in_bounds(p, base + (long long)row * p.ldc, 8))
+                    multimem_st_v4(dst + base + (long long)row * p.ldc, regs[i]);
             }
             continue;
         }
@@ -192,7 +204,7 @@ __device__ __forceinline__ void epilogue_band_multi(const GemmParams &p, const S
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const int row = row0 + 2 * i + (lane >> 4);
-                if (row < p.M) {
+                if (row < p.M && ccol < p.N && store_in_bounds(p, base + (long long)row * p.ldc, min(8, p.N - ccol))) {
                     uint16_t *q = dst + base + (long long)row * p.ldc;
                     if (ccol + 8 <= p.N) {
                         *reinterpret_cast<uint4 *>(q) = regs[i];

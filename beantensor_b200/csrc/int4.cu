@@ -765,7 +765,7 @@ int configure_int4_gemv_kernels()
     if (e == cudaSuccess) e = cudaFuncSetAttribute(int4_gemv_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 150 * 1024);
     int rc = check_cuda(e, "cudaFuncSetAttribute(int4_gemv_stream)");
     if (rc) return rc;
-    return configure_int4_gemv_rows_kernels();
+    return configure_int4_gemv_regs_kernels();
 }
 
 int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
@@ -807,14 +807,14 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
         if (rc) return rc;
         return check_cuda(cudaGetLastError(), "int4 gemm launch");
     }
-    // Few rows (M <= 3): the register-resident kernel (int4_gemv_rows.cu), 7.2 us against 9.1 us at M = 1 and 8.1 against
+    // Few rows (M <= 3): the register-resident kernel (int4_gemv_regs.cu), 7.2 us against 9.1 us at M = 1 and 8.1 against
     // 9.2 us at M = 2 on the 11008 x 4096 workload; at M = 4 the two are level (9.5 us) and at M = 8 its per-CTA
     // activation staging costs more than it gains (12.3 against 11.1 us), so more rows stay on the streaming kernel below. BTM_FORCE_GEMV=regs|stream|slab pins a
     // kernel (the tests use it to run every kernel on every shape it takes). Shapes a kernel does not take fall through.
     const char *force_gemv = getenv("BTM_FORCE_GEMV");
     const bool want_regs = force_gemv ? !strcmp(force_gemv, "regs") : M <= 3;
     if (want_regs) {
-        const int rc_regs = launch_int4_gemv_rows(st, sm_count, M, N, K, group, act, w, scales, out);
+        const int rc_regs = launch_int4_gemv_regs(st, sm_count, M, N, K, group, act, w, scales, out);
         if (rc_regs != -1) return rc_regs;
     }
     const bool stage_act = M <= 2; // slab kernel: a slab and more than two staged rows do not fit together

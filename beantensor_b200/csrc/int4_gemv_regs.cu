@@ -249,7 +249,7 @@ size_t regs_smem_bytes(int M, int K)
 
 } // namespace
 
-int configure_int4_gemv_rows_kernels()
+int configure_int4_gemv_regs_kernels()
 {
     return check_cuda(cudaFuncSetAttribute(int4_gemv_regs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024),
                       "cudaFuncSetAttribute(int4_gemv_regs)");
@@ -258,7 +258,7 @@ int configure_int4_gemv_rows_kernels()
 // Returns a btm_status, or -1 when the shape is outside what this kernel takes (nothing launched, no error set):
 // M in 1..8 with the staged activations within half an SM's shared memory, K a multiple of 512 up to 4096, group 128,
 // 16-byte aligned weights and activations, 8-byte aligned scales.
-int launch_int4_gemv_rows(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
+int launch_int4_gemv_regs(cudaStream_t st, int sm_count, int M, int N, int K, int group, const void *act, const void *w,
                           const void *scales, void *out)
 {
     if (M < 1 || M > 8 || N < 1 || group != 128 || K < 512 || (K % 512) || K > 128 * GR_W * GR_NB) return -1;

@@ -98,7 +98,11 @@ const char *btm_last_error_string(void);
  * matmul kernels observable without any fault: "wait_limit_cycles" (SM cycles after which a kernel wait gives
  * up; 0 restores the default of about one second) and "skip_loads" (non-zero: the producer warps of the dense
  * matmul kernels issue no loads, so the consumers' waits run out, the kernel unwinds, returns, and the next
- * btm_check_device_status reports BTM_ERR_TIMEOUT). Unknown keys return BTM_ERR_INVALID. */
+ * btm_check_device_status reports BTM_ERR_TIMEOUT); "bounds" (non-zero: every store address that a matmul epilogue
+ * computes by hand is compared with the extent of C first, a store that would leave it is skipped and reported by
+ * btm_check_device_status as BTM_ERR_CUDA; also switched on by the environment variable BTM_DEBUG_BOUNDS=1, read once)
+ * and "bounds_shrink" (pretend C is that many elements shorter, so that a test can watch the check fire without any
+ * access outside memory). Unknown keys return BTM_ERR_INVALID. */
 int btm_debug_set(const char *key, long long value);
 
 /* Prepare `device`: checks that it is an sm_100 part, creates the per-device state
