@@ -807,12 +807,12 @@ int launch_int4_gemv(cudaStream_t st, int sm_count, int M, int N, int K, int gro
         if (rc) return rc;
         return check_cuda(cudaGetLastError(), "int4 gemm launch");
     }
-    // Few rows (M <= 3): the register-resident kernel (int4_gemv_regs.cu), 7.2 us against 9.1 us at M = 1 and 8.1 against
-    // 9.2 us at M = 2 on the 11008 x 4096 workload; at M = 4 the two are level (9.5 us) and at M = 8 its per-CTA
-    // activation staging costs more than it gains (12.3 against 11.1 us), so more rows stay on the streaming kernel below. BTM_FORCE_GEMV=regs|stream|slab pins a
-    // kernel (the tests use it to run every kernel on every shape it takes). Shapes a kernel does not take fall through.
+    // M <= 8: the register-resident kernel (int4_gemv_regs.cu) wherever it takes the shape. On the 11008 x 4096 workload
+    // it runs 7.1 / 7.6 / 8.5 / 9.9 us at M = 1 / 2 / 4 / 8 against 9.1 / 9.2 / 9.4 / 11.0 us for the streaming kernel
+    // below. BTM_FORCE_GEMV=regs|stream|slab pins a kernel (the tests use it to run every kernel on every shape it
+    // takes). Shapes a kernel does not take fall through to the next.
     const char *force_gemv = getenv("BTM_FORCE_GEMV");
-    const bool want_regs = force_gemv ? !strcmp(force_gemv, "regs") : M <= 3;
+    const bool want_regs = force_gemv ? !strcmp(force_gemv, "regs") : true;
     if (want_regs) {
         const int rc_regs = launch_int4_gemv_regs(st, sm_count, M, N, K, group, act, w, scales, out);
         if (rc_regs != -1) return rc_regs;

@@ -1,4 +1,4 @@
-// int4 weight-only GEMV for few activation rows (M <= 4), register-resident form.
+// int4 weight-only GEMV for M <= 8 activation rows, register-resident form.
 //
 // The kernel is a weight stream: N*K/2 bytes are read once and every byte is used once. What it has to get right
 // is (a) how many bytes it keeps in flight from HBM and (b) how few instructions it spends per byte, because on
@@ -11,7 +11,8 @@
 //     into registers. There is no shared-memory ring and no mbarrier. Every warp holds TWO register buffers: the
 //     loads of the group after next are issued as soon as a buffer has been consumed, so two groups per CTA
 //     (128 KB per SM) are in flight while a third is being multiplied.
-//   * The activations are staged once per CTA, permuted to the slot order in which the nibbles of a 32-bit word
+//   * The activations are staged once per CTA (every warp the K slice it will use itself, so no CTA barrier precedes
+//     the first product), permuted to the slot order in which the nibbles of a 32-bit word
 //     fall out of two masks and a shift: 8 consecutive values a0..a7 become {a0,a4} {a1,a5}/16 {a2,a6} {a3,a7}/16
 //     (the k order inside an mma is free as long as both operands agree).
 //   * The nibbles are NOT converted to their signed values. (x & 0x000F000F) ^ 0x64086408 is the fp16 pair
@@ -111,29 +112,33 @@ int4_gemv_regs_kernel(const uint8_t *__restrict__ w, int M, int N, int K, const 
     if (rgB < nrg) issue_loads(rgB, qa1, qb1, sv1);
 
     // ---------------------------------------------------------------- activations (after the predecessor has finished)
+    // Every warp stages the activations of its own K slice (its NB blocks of every row) and nothing else, so the warps
+    // do not meet on a CTA barrier before their first product: one round trip to L2, a permute, and the warp goes on.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    {
-        const int per_row = K >> 3; // uint4 (8 activations) per row
-        const int total = M * per_row;
-        for (int i = threadIdx.x; i < nkb * 16; i += GR_THREADS) // rows m >= M of the corrections: never stored, but defined
-            if ((((i >> 2) & 3) * 2 + (i & 1)) >= M) reinterpret_cast<float *>(corr_s)[i] = 0.0f;
+    if (active) {
+        const int per_row = K >> 3;          // uint4 (8 activations) per row
+        constexpr int PER_WARP = NB * 16;    // uint4 of one row that belong to this warp's blocks
         const __half2 sixteenth = __half2half2(__ushort_as_half((unsigned short)0x2C00));
-        constexpr int UN = 2; // loads in flight per thread
-        for (int base0 = warp * 32; base0 < total; base0 += GR_THREADS * UN) {
+        for (int i = lane; i < NB * 16; i += 32) // corrections of rows m >= M: never stored, but defined
+            if ((((i >> 2) & 3) * 2 + (i & 1)) >= M) reinterpret_cast<float *>(corr_s + kb0 * 4)[i] = 0.0f;
+        constexpr int UN = 4; // loads in flight per lane
+        const int total = M * PER_WARP;
+        for (int base0 = 0; base0 < total; base0 += 32 * UN) {
             uint4 vv[UN];
 #pragma unroll
             for (int u = 0; u < UN; ++u) {
-                const int i = base0 + u * GR_THREADS + lane;
+                const int i = base0 + u * 32 + lane;
+                const int m = i / PER_WARP, r = i - m * PER_WARP;
                 vv[u] = make_uint4(0u, 0u, 0u, 0u);
-                if (i < total) vv[u] = __ldg(reinterpret_cast<const uint4 *>(act) + i);
+                if (i < total) vv[u] = __ldg(reinterpret_cast<const uint4 *>(act) + (size_t)m * per_row + kb0 * 16 + r);
             }
 #pragma unroll
             for (int u = 0; u < UN; ++u) {
-                const int i = base0 + u * GR_THREADS + lane;
+                const int i = base0 + u * 32 + lane;
                 const bool valid = i < total;
+                const int m = i / PER_WARP, r = i - m * PER_WARP;
+                const int kb = kb0 + (r >> 4), tt = (r >> 2) & 3, wd = r & 3;
                 const uint4 v = vv[u];
-                const int m = i / per_row, r = i - m * per_row;
-                const int kb = r >> 4, tt = (r >> 2) & 3, wd = r & 3;
                 uint4 o;
                 o.x = __byte_perm(v.x, v.z, 0x5410);
                 uint32_t b15 = __byte_perm(v.x, v.z, 0x7632);
@@ -160,7 +165,7 @@ int4_gemv_regs_kernel(const uint8_t *__restrict__ w, int M, int N, int K, const 
             }
         }
     }
-    __syncthreads();
+    __syncwarp();
 
     // Lane (g, t) supplies activation row g to the mma's B operand; output columns m >= M are never stored, so
     // those lanes simply read the last row again.
