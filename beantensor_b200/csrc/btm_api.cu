@@ -220,6 +220,7 @@ static int run_16bit(DeviceState *ds, cudaStream_t st, const GemmCall &c)
     p.K = c.K;
     p.batch = c.batch;
     p.group_m = 8;
+    if (const char *gm = getenv("BTM_GROUP_M")) p.group_m = std::max(1, atoi(gm)); // tile raster: m-tiles per L2 group (tuning aid)
     p.ndst = c.ndst;
     bool vec = (c.ldc * (long long)es) % 16 == 0 && (c.col0 * (long long)es) % 16 == 0 &&
                (c.batch == 1 || (c.strideC * (long long)es) % 16 == 0);
