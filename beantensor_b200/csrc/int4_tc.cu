@@ -79,9 +79,10 @@ constexpr int OUT_TILE_OFF = (MAX_SPLIT - 1) * RED_BYTES; // fp16 [64 m][128 n] 
 template <int MB> // activation rows per pass: 64 or 128 (= UMMA N = accumulator columns)
 struct Cfg {
     static constexpr int RAW_STAGES = MB == 64 ? 6 : 4;
-    static constexpr int ACT_STAGES = MB == 64 ? 6 : 4;
     static constexpr int W_STAGES = (TMEM_COLS - MB) / W_COLS; // 3 or 2 units in tensor memory
-    static constexpr int ACT_BYTES = MB * 128;
+    static constexpr int ACT_STAGES = W_STAGES;                // one activation stage (128 k) per unit in tensor memory
+    static constexpr int ACT_HALF = MB * 128;                  // one 64-k block: MB rows of 128 bytes
+    static constexpr int ACT_BYTES = 2 * ACT_HALF;
     static constexpr int RING_BYTES = ACT_STAGES * ACT_BYTES + RAW_STAGES * RAW_BYTES;
     // After the main loop the rings are dead and hold the parked accumulator (MB x 128 fp32) or, in CTA 0, the output tile.
     static_assert(OUT_TILE_OFF + RED_COLS * BW * 2 <= RING_BYTES && MB * BW * 4 <= RING_BYTES, "reduction buffers must fit in the rings");
@@ -130,7 +131,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     constexpr int RAW_STAGES = C::RAW_STAGES, ACT_STAGES = C::ACT_STAGES, W_STAGES = C::W_STAGES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_raw_full[RAW_STAGES], bar_raw_empty[RAW_STAGES];
-    __shared__ __align__(8) uint64_t bar_act_full[ACT_STAGES], bar_act_empty[ACT_STAGES], bar_w_full[W_STAGES], bar_w_empty[W_STAGES];
+    __shared__ __align__(8) uint64_t bar_act_full[ACT_STAGES], bar_w_full[W_STAGES], bar_w_empty[W_STAGES];
     __shared__ __align__(8) uint64_t bar_acc_full;
     __shared__ uint32_t tmem_base_holder;
     __shared__ int abort_flag;
@@ -198,11 +199,8 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             mbar_init(smem_u32(&bar_raw_full[i]), 1);
             mbar_init(smem_u32(&bar_raw_empty[i]), 4);
         }
-        for (int i = 0; i < ACT_STAGES; ++i) {
-            mbar_init(smem_u32(&bar_act_full[i]), 1);
-            mbar_init(smem_u32(&bar_act_empty[i]), 1);
-        }
         for (int i = 0; i < W_STAGES; ++i) {
+            mbar_init(smem_u32(&bar_act_full[i]), 1);
             mbar_init(smem_u32(&bar_w_full[i]), 4);
             mbar_init(smem_u32(&bar_w_empty[i]), 1);
         }
@@ -240,47 +238,41 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     } else if (warp == 2) {
         // ------------------------------------------------------------ TMA producer: activation tiles
         if (lane == 0) {
+            // Stage ws of the activations lives and dies with stage ws of the unpacked weights: the commit that
+            // frees the unit in tensor memory (bar_w_empty) frees its activations too.
             int as = 0;
             uint32_t aphase = 0;
-            bool ok = true;
-            for (int i = 0; ok && i < n_units; ++i) {
+            for (int i = 0; i < n_units; ++i) {
                 const int u = unit_at(i);
-                for (int q = 0; q < UNIT_K / BKE; ++q) {
-                    if (!mbar_wait(smem_u32(&bar_act_empty[as]), aphase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
-                        ok = false;
-                        break;
-                    }
-                    mbar_expect_tx(smem_u32(&bar_act_full[as]), C::ACT_BYTES);
-                    tma_load_3d(act_ring + as * C::ACT_BYTES, &tmAct, (u * 2 + q) * BKE, m_base, 0, smem_u32(&bar_act_full[as]));
-                    if (++as == ACT_STAGES) { as = 0; aphase ^= 1u; }
-                }
+                if (!mbar_wait(smem_u32(&bar_w_empty[as]), aphase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) break;
+                mbar_expect_tx(smem_u32(&bar_act_full[as]), C::ACT_BYTES);
+                tma_load_3d(act_ring + as * C::ACT_BYTES, &tmAct, u * UNIT_K, m_base, 0, smem_u32(&bar_act_full[as]));
+                tma_load_3d(act_ring + as * C::ACT_BYTES + C::ACT_HALF, &tmAct, u * UNIT_K + BKE, m_base, 0, smem_u32(&bar_act_full[as]));
+                if (++as == ACT_STAGES) { as = 0; aphase ^= 1u; }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(0u /*F16*/, false, false, BW, MB);
-            int as = 0, ws = 0;
-            uint32_t aphase = 0, wphase = 0;
+            int ws = 0;
+            uint32_t wphase = 0;
             bool ok = true;
-            for (int i = 0; ok && i < n_units; ++i) {
-                if (!mbar_wait_short(smem_u32(&bar_w_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL)) break;
-                for (int q = 0; q < UNIT_K / BKE; ++q) {
-                    if (!mbar_wait_short(smem_u32(&bar_act_full[as]), aphase, &abort_flag, p.status, WAIT_MMA_FULL)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t w0 = tmem_base + (uint32_t)(MB + ws * W_COLS + q * 32), a0 = act_ring + as * C::ACT_BYTES;
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t ad = make_smem_desc_sw128(a0 + ks * 32, 16, 1024);
-                        umma_a_tmem(tmem_base, w0 + (uint32_t)(ks * 8), ad, idesc, (i | q | ks) ? 1u : 0u);
-                    }
-                    umma_commit(smem_u32(&bar_act_empty[as])); // the activation tile is free once these MMAs have read it
-                    if (++as == ACT_STAGES) { as = 0; aphase ^= 1u; }
+            for (int i = 0; i < n_units; ++i) {
+                // The activations come from L2 and are there long before the unit is unpacked: ask for them first.
+                if (!mbar_wait_short(smem_u32(&bar_act_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL) ||
+                    !mbar_wait_short(smem_u32(&bar_w_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL)) {
+                    ok = false;
+                    break;
                 }
-                umma_commit(smem_u32(&bar_w_empty[ws])); // ... and the unit in tensor memory after both of its blocks
+                tc_fence_after();
+                const uint32_t w0 = tmem_base + (uint32_t)(MB + ws * W_COLS), a0 = act_ring + ws * C::ACT_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint64_t ad = make_smem_desc_sw128(a0 + (ks >> 2) * C::ACT_HALF + (ks & 3) * 32, 16, 1024);
+                    umma_a_tmem(tmem_base, w0 + (uint32_t)(ks * 8), ad, idesc, (i | ks) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&bar_w_empty[ws])); // the unit in tensor memory and its activations are free
                 if (++ws == W_STAGES) { ws = 0; wphase ^= 1u; }
             }
             if (ok) umma_commit(smem_u32(&bar_acc_full));
