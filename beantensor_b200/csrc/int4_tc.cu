@@ -8,11 +8,12 @@
 // no tensor-core row is spent on padding when M is small. K is split over the CTAs of a cluster, which
 // puts two or three times as many CTAs on the machine as there are 128-row weight tiles (86 for
 // N = 11008) and divides the activation bytes a CTA pulls from L2 by the same factor; the partial
-// accumulators meet in the shared memory of the cluster's first CTA.
+// accumulators are summed over the cluster's shared memory, every CTA taking a share of the activation rows.
 //
 // Roles in a CTA (11 warps), per 128-k unit of its K slice:
 //   warp 0      TMA: packed weights, 128 rows x 64 B (64-byte swizzle), ring of 4-6 units;
-//   warp 2      TMA: activation tiles, MB rows x 64 k (K-major, 128-byte swizzle), two per unit;
+//   warp 2      TMA: activation tiles, MB rows x 64 k (K-major, 128-byte swizzle), two per unit, in a stage that
+//               is tied to the unit's stage in tensor memory (filled and freed together);
 //   warps 3-10  dequantise: thread = weight row, the two groups of four warps take alternate units; four
 //               128-bit shared loads, unpack to exact fp16 integers in natural k order, multiply by
 //               the group scale, and write the row's 128 fp16 straight into tensor memory (tcgen05.st,
@@ -20,13 +21,14 @@
 //               there, so the tile never passes through shared memory and needs no proxy fence. A
 //               warp passes one set of hand-offs per 128 k; those hand-offs, not arithmetic or
 //               bandwidth, are what the kernel's time is made of;
-//   warp 1      tcgen05.mma (M = 128, N = MB, A from tensor memory, B K-major in shared memory);
-//               tcgen05.commit frees the activation tile after each 64-k block and the unit in
-//               tensor memory after both.
-// Then CTAs 1.. of the cluster park their accumulator (lane = weight row, column = activation row) in
-// their own shared memory, and after one cluster barrier CTA 0 fetches the parked values over DSMEM,
-// adds them to its own in rank order, rounds once to fp16, transposes the tile through shared memory
-// and stores rows of 256 contiguous bytes of out[m, n0 .. n0 + 128).
+//   warp 1      tcgen05.mma (M = 128, N = MB, A from tensor memory, B K-major in shared memory): one wait,
+//               eight MMAs and one tcgen05.commit per unit (the commit frees the unit in tensor memory and
+//               its activations). Its issue is serial and shares the tensor pipe with the SM's other CTA,
+//               so everything else has been moved off this thread.
+// Then every CTA parks its accumulator (lane = weight row, column = activation row) in its own shared
+// memory, and after one cluster barrier CTA r fetches block r of the columns from all CTAs over DSMEM,
+// adds them in rank order, rounds once to fp16, transposes through shared memory and stores rows of 256
+// contiguous bytes of out[m, n0 .. n0 + 128) for its block of m.
 // HBM traffic: the packed weights once (N*K/2 bytes) plus scales; activations come from L2
 // (N/128 x M x K x 2 bytes in total, whatever the split).
 #include <cuda_fp16.h>
@@ -72,10 +74,6 @@ constexpr int TMEM_COLS = 256;     // accumulator (MB columns) + ring of dequant
 constexpr int THREADS = 352;       // warp 0 weight TMA, 1 MMA, 2 activation TMA, 3..10 dequantise + epilogue
 constexpr int DQ_FIRST = 96;       // first dequantising thread
 constexpr int MAX_SPLIT = 3;
-constexpr int RED_COLS = 64;       // accumulator columns reduced per round
-constexpr int RED_FLOATS = RED_COLS * BW;
-constexpr int RED_BYTES = RED_FLOATS * 4; // one CTA's partials for one round (32 KB)
-constexpr int OUT_TILE_OFF = (MAX_SPLIT - 1) * RED_BYTES; // fp16 [64 m][128 n] staging behind the partials
 template <int MB> // activation rows per pass: 64 or 128 (= UMMA N = accumulator columns)
 struct Cfg {
     static constexpr int RAW_STAGES = MB == 64 ? 6 : 4;
@@ -84,8 +82,8 @@ struct Cfg {
     static constexpr int ACT_HALF = MB * 128;                  // one 64-k block: MB rows of 128 bytes
     static constexpr int ACT_BYTES = 2 * ACT_HALF;
     static constexpr int RING_BYTES = ACT_STAGES * ACT_BYTES + RAW_STAGES * RAW_BYTES;
-    // After the main loop the rings are dead and hold the parked accumulator (MB x 128 fp32) or, in CTA 0, the output tile.
-    static_assert(OUT_TILE_OFF + RED_COLS * BW * 2 <= RING_BYTES && MB * BW * 4 <= RING_BYTES, "reduction buffers must fit in the rings");
+    // After the main loop the rings are dead and hold the parked accumulator (MB x 128 fp32) and behind it the output tile.
+    static_assert(MB * BW * 4 + MB * BW * 2 <= RING_BYTES, "parked accumulator and output tile must fit in the rings");
     static constexpr int SMEM_BYTES = RING_BYTES + 1024; // + BW * groups-in-slice * 2 bytes of scales at run time
 };
 constexpr int SCALE_SMEM_MAX = 6144;
@@ -259,9 +257,9 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             uint32_t wphase = 0;
             bool ok = true;
             for (int i = 0; i < n_units; ++i) {
-                // The activations come from L2 and are there long before the unit is unpacked: ask for them first.
-                if (!mbar_wait_short(smem_u32(&bar_act_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL) ||
-                    !mbar_wait_short(smem_u32(&bar_w_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL)) {
+                // One wait per unit: the first dequantising warp of the unit's group has seen the unit's activations
+                // arrive before it reports its rows (below), so this barrier covers both operands.
+                if (!mbar_wait_short(smem_u32(&bar_w_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL)) {
                     ok = false;
                     break;
                 }
@@ -355,6 +353,12 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             tmem_st_32x32(tmem_row + (uint32_t)(ws * W_COLS + 32), *reinterpret_cast<const uint32_t(*)[32]>(&d[0]));
             tmem_st_wait();
             tc_fence_before();
+            // The activations of the unit come from L2 and have been there for a while; the warp that vouches for
+            // them takes this off the MMA issuer's serial path.
+            if ((warp & 3) == 3) {
+                ok = mbar_wait_short_warp(smem_u32(&bar_act_full[ws]), (uint32_t)((i / W_STAGES) & 1), &abort_flag, p.status, WAIT_EPI_STAGE);
+                if (!ok) break;
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_w_full[ws]));
         }
@@ -367,18 +371,18 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     __syncthreads(); // this CTA's rings are dead: its tensor-core and TMA traffic is over
     const bool acc_ok = abort_flag == 0; // the same answer in every thread of the CTA
     const bool epi = warp >= 3;
-    const int quad = warp & 3;         // the tensor-memory lanes this warp may read
-    const int erow = quad * 32 + lane; // accumulator lane = weight row of the tile
-    const int chalf = (warp - 3) >> 2; // which 32 of a round's 64 columns
-    float *park = reinterpret_cast<float *>(smem_al); // [MB columns][128 rows] fp32 over the dead rings
-    // CTAs 1.. park their accumulator in their own shared memory (column-major: a warp writes 128 contiguous
-    // bytes); CTA 0 fetches it from there after the barrier. Nothing is written into another CTA's memory, so
-    // no CTA has to wait for another one's main loop before it may start.
-    if (epi && crank != 0) {
+    // Every CTA parks its accumulator in its own shared memory ([column = activation row][128 weight rows] fp32, a
+    // warp writes 128 contiguous bytes); after one cluster barrier CTA r sums block r of the columns over all CTAs
+    // of the cluster (always in rank order, so the sum does not depend on who adds or when) and stores those rows
+    // of the output. Nothing is written into another CTA's memory, and the reduction, the conversion and the
+    // stores are spread over the cluster instead of queued in its first CTA.
+    const int valid = min(MB, p.M - m_base); // columns that hold rows of the activations; the rest is padding
+    float *park = reinterpret_cast<float *>(smem_al);
+    if (epi) {
+        const int quad = warp & 3, erow = quad * 32 + lane; // the tensor-memory lanes this warp may read
 #pragma unroll 1
-        for (int h = 0; h < MB / RED_COLS; ++h) {
+        for (int col0 = ((warp - 3) >> 2) * 32; col0 < valid; col0 += 64) {
             uint32_t v[32];
-            const int col0 = h * RED_COLS + chalf * 32;
             tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, v);
             tmem_ld_wait();
 #pragma unroll
@@ -386,56 +390,57 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         }
     }
     cluster_sync_all(); // every accumulator of the cluster is parked and visible (release / acquire)
-    if (epi && crank == 0 && acc_ok) {
-        uint16_t *tile_out = reinterpret_cast<uint16_t *>(smem_al + OUT_TILE_OFF);
+    if (epi && acc_ok) {
+        const int t = threadIdx.x - DQ_FIRST, row = t & (BW - 1), half = t >> 7;
+        const int per = (((valid + 7) >> 3) + (int)csize - 1) / (int)csize * 8; // columns per CTA, a multiple of 8
+        const int c_lo = min(valid, (int)crank * per), c_hi = min(valid, c_lo + per);
+        uint16_t *tile_out = reinterpret_cast<uint16_t *>(smem_al + MB * BW * 4); // fp16 [column][128 n] behind the parked values
         uint16_t *out = reinterpret_cast<uint16_t *>(p.C[0]);
         const bool vec_store = (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        uint32_t src[MAX_SPLIT];
+#pragma unroll
+        for (int r = 0; r < MAX_SPLIT; ++r) src[r] = map_to_cta(smem_base + (uint32_t)row * 4u, (uint32_t)(r < (int)csize ? r : 0));
 #pragma unroll 1
-        for (int h = 0; h < MB / RED_COLS; ++h) {
-            uint32_t v[32];
-            const int col0 = h * RED_COLS + chalf * 32;
-            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, v);
-            tmem_ld_wait();
-            float acc[32];
+        for (int c0 = c_lo + half; c0 < c_hi; c0 += 8) {
+            float x[4][MAX_SPLIT];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) acc[c] = __uint_as_float(v[c]);
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t off = (uint32_t)(c0 + 2 * j) * (BW * 4);
 #pragma unroll
-            for (int r = 1; r < MAX_SPLIT; ++r) { // rank order: the sum does not depend on timing
-                if (r < (int)csize) {
-                    const uint32_t src = map_to_cta(smem_base + (uint32_t)(col0 * BW + erow) * 4u, (uint32_t)r);
-                    float x[32];
+                for (int r = 0; r < MAX_SPLIT; ++r)
+                    if (c0 + 2 * j < c_hi && r < (int)csize) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x[j][r]) : "r"(src[r] + off));
+            }
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x[c]) : "r"(src + (uint32_t)c * (BW * 4)));
+            for (int j = 0; j < 4; ++j) {
+                if (c0 + 2 * j < c_hi) {
+                    float acc = x[j][0];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) acc[c] += x[c];
+                    for (int r = 1; r < MAX_SPLIT; ++r)
+                        if (r < (int)csize) acc += x[j][r];
+                    tile_out[(c0 + 2 * j - c_lo) * BW + row] = __half_as_ushort(__float2half_rn(acc));
                 }
             }
-            // fp16 tile [64 m][128 n] in shared memory, then rows of 256 contiguous bytes to global memory
-            if (h > 0) asm volatile("bar.sync 1, 256;" ::: "memory"); // the previous round's tile has been read
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        // rows of 256 contiguous bytes to global memory
+        const int chunk = t & 15, n = n0 + chunk * 8;
+        for (int mt = t >> 4; mt < c_hi - c_lo; mt += 16) {
+            const int m = m_base + c_lo + mt;
+            if (n < p.N) {
+                const uint4 val = *reinterpret_cast<const uint4 *>(tile_out + mt * BW + chunk * 8);
+                uint16_t *dst = out + (long long)m * p.ldc + n;
+                if (vec_store && n + 8 <= p.N) {
+                    *reinterpret_cast<uint4 *>(dst) = val;
+                } else {
+                    const uint32_t w[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
-            for (int c = 0; c < 32; ++c) tile_out[(chalf * 32 + c) * BW + erow] = __half_as_ushort(__float2half_rn(acc[c]));
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            const int t = threadIdx.x - DQ_FIRST;
-            const int chunk = t & 15, n = n0 + chunk * 8;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int mt = (t >> 4) + 16 * k, m = m_base + h * RED_COLS + mt;
-                if (m < p.M && n < p.N) {
-                    const uint4 val = *reinterpret_cast<const uint4 *>(tile_out + mt * BW + chunk * 8);
-                    uint16_t *dst = out + (long long)m * p.ldc + n;
-                    if (vec_store && n + 8 <= p.N) {
-                        *reinterpret_cast<uint4 *>(dst) = val;
-                    } else {
-                        const uint32_t w[4] = {val.x, val.y, val.z, val.w};
-#pragma unroll
-                        for (int e = 0; e < 8; ++e)
-                            if (n + e < p.N) dst[e] = (uint16_t)((e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xFFFFu));
-                    }
+                    for (int e = 0; e < 8; ++e)
+                        if (n + e < p.N) dst[e] = (uint16_t)((e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xFFFFu));
                 }
             }
         }
     }
-    cluster_sync_all(); // CTA 0 has read the parked accumulators: their owners may exit
+    cluster_sync_all(); // every CTA has read what it needs of the others' parked accumulators: their owners may exit
 
     tc_fence_before();
     __syncthreads();
