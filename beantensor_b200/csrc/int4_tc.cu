@@ -191,6 +191,11 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         }
     }
 
+    // Programmatic dependent launch: this grid lets its successor on the stream start as soon as the machine has
+    // room for its CTAs. Weights and scales are constants, so a CTA may fetch them while its predecessor still runs;
+    // the activations are read and the output is written only after griddepcontrol.wait (warp 2 and the epilogue).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     if (warp == 0 && lane == 0) {
         abort_flag = 0;
         for (int i = 0; i < RAW_STAGES; ++i) {
@@ -240,6 +245,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             // frees the unit in tensor memory (bar_w_empty) frees its activations too.
             int as = 0;
             uint32_t aphase = 0;
+            asm volatile("griddepcontrol.wait;" ::: "memory"); // the activations may be the predecessor's output
             for (int i = 0; i < n_units; ++i) {
                 const int u = unit_at(i);
                 if (!mbar_wait(smem_u32(&bar_w_empty[as]), aphase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) break;
@@ -390,6 +396,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         }
     }
     cluster_sync_all(); // every accumulator of the cluster is parked and visible (release / acquire)
+    if (epi) asm volatile("griddepcontrol.wait;" ::: "memory"); // long since true; orders this grid's stores behind the predecessor
     if (epi && acc_ok) {
         const int t = threadIdx.x - DQ_FIRST, row = t & (BW - 1), half = t >> 7;
         const int per = (((valid + 7) >> 3) + (int)csize - 1) / (int)csize * 8; // columns per CTA, a multiple of 8
@@ -504,13 +511,15 @@ int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const v
         cfg.gridDim = dim3((unsigned)(tiles * split), 1, 1);
         cfg.blockDim = dim3(THREADS, 1, 1);
         cfg.stream = st;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = (unsigned)split;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; // the kernel orders itself with griddepcontrol
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = 2;
         cudaError_t e;
         if (mb == 64) {
             cfg.dynamicSmemBytes = Cfg<64>::SMEM_BYTES + sc_bytes;
