@@ -122,7 +122,7 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta)
 template <int MB>
 __global__ void __launch_bounds__(i4tc::THREADS, 2)
 int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ CUtensorMap tmW, const GemmParams p,
-                    const __half *__restrict__ scales, int group, int m_base)
+                    const __half *__restrict__ scales, int group, int m_base, int n_inst)
 {
     using namespace i4tc;
     using C = Cfg<MB>;
@@ -249,7 +249,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             for (int i = 0; i < n_units; ++i) {
                 const int u = unit_at(i);
                 if (!mbar_wait(smem_u32(&bar_w_empty[as]), aphase ^ 1u, &abort_flag, p.status, WAIT_PRODUCER_EMPTY)) break;
-                mbar_expect_tx(smem_u32(&bar_act_full[as]), C::ACT_BYTES);
+                mbar_expect_tx(smem_u32(&bar_act_full[as]), (uint32_t)n_inst * 256u); // two blocks of n_inst rows x 128 bytes
                 tma_load_3d(act_ring + as * C::ACT_BYTES, &tmAct, u * UNIT_K, m_base, 0, smem_u32(&bar_act_full[as]));
                 tma_load_3d(act_ring + as * C::ACT_BYTES + C::ACT_HALF, &tmAct, u * UNIT_K + BKE, m_base, 0, smem_u32(&bar_act_full[as]));
                 if (++as == ACT_STAGES) { as = 0; aphase ^= 1u; }
@@ -258,7 +258,9 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(0u /*F16*/, false, false, BW, MB);
+            // UMMA N = the activation rows of this pass rounded up to 16: the tensor pipe's time per instruction grows
+            // with N, and it is shared with the SM's other CTA.
+            const uint32_t idesc = make_idesc(0u /*F16*/, false, false, BW, (uint32_t)n_inst);
             int ws = 0;
             uint32_t wphase = 0;
             bool ok = true;
@@ -397,13 +399,11 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     }
     cluster_sync_all(); // every accumulator of the cluster is parked and visible (release / acquire)
     if (epi) asm volatile("griddepcontrol.wait;" ::: "memory"); // long since true; orders this grid's stores behind the predecessor
+    const int t = threadIdx.x - DQ_FIRST, row = t & (BW - 1), half = t >> 7;
+    const int per = (((valid + 7) >> 3) + (int)csize - 1) / (int)csize * 8; // columns per CTA, a multiple of 8
+    const int c_lo = min(valid, (int)crank * per), c_hi = min(valid, c_lo + per);
+    uint16_t *tile_out = reinterpret_cast<uint16_t *>(smem_al + MB * BW * 4); // fp16 [column][128 n] behind the parked values
     if (epi && acc_ok) {
-        const int t = threadIdx.x - DQ_FIRST, row = t & (BW - 1), half = t >> 7;
-        const int per = (((valid + 7) >> 3) + (int)csize - 1) / (int)csize * 8; // columns per CTA, a multiple of 8
-        const int c_lo = min(valid, (int)crank * per), c_hi = min(valid, c_lo + per);
-        uint16_t *tile_out = reinterpret_cast<uint16_t *>(smem_al + MB * BW * 4); // fp16 [column][128 n] behind the parked values
-        uint16_t *out = reinterpret_cast<uint16_t *>(p.C[0]);
-        const bool vec_store = (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
         uint32_t src[MAX_SPLIT];
 #pragma unroll
         for (int r = 0; r < MAX_SPLIT; ++r) src[r] = map_to_cta(smem_base + (uint32_t)row * 4u, (uint32_t)(r < (int)csize ? r : 0));
@@ -428,6 +428,13 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
                 }
             }
         }
+    }
+    // This thread has read what it needs of the other CTAs' shared memory: tell them now and wait for them at the
+    // very end, so that the conversion barrier and the global stores do not sit in front of anybody's exit.
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    if (epi && acc_ok) {
+        uint16_t *out = reinterpret_cast<uint16_t *>(p.C[0]);
+        const bool vec_store = (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
         asm volatile("bar.sync 1, 256;" ::: "memory");
         // rows of 256 contiguous bytes to global memory
         const int chunk = t & 15, n = n0 + chunk * 8;
@@ -447,7 +454,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             }
         }
     }
-    cluster_sync_all(); // every CTA has read what it needs of the others' parked accumulators: their owners may exit
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); // every CTA has read what it needs of this one's parked accumulator
 
     tc_fence_before();
     __syncthreads();
@@ -494,7 +501,8 @@ int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const v
     for (int m_base = 0; m_base < M; m_base += 128) {
         const int rows = M - m_base < 128 ? M - m_base : 128;
         const int mb = rows <= 64 ? 64 : 128;
-        rc = encode_tmap_3d(&tmAct, BTM_F16, act, (uint64_t)K, (uint64_t)M, 1, (uint64_t)K * 2, (uint64_t)K * 2, 64, (uint32_t)mb);
+        const int n_inst = (rows + 15) / 16 * 16; // rows the activation tiles carry and the MMAs multiply
+        rc = encode_tmap_3d(&tmAct, BTM_F16, act, (uint64_t)K, (uint64_t)M, 1, (uint64_t)K * 2, (uint64_t)K * 2, 64, (uint32_t)n_inst);
         if (rc) return rc;
         GemmParams p;
         memset(&p, 0, sizeof(p));
@@ -523,10 +531,10 @@ int launch_int4_gemm_tc(cudaStream_t st, int M, int N, int K, int group, const v
         cudaError_t e;
         if (mb == 64) {
             cfg.dynamicSmemBytes = Cfg<64>::SMEM_BYTES + sc_bytes;
-            e = cudaLaunchKernelEx(&cfg, int4_gemm_tc_kernel<64>, tmAct, tmW, p, (const __half *)scales, group, m_base);
+            e = cudaLaunchKernelEx(&cfg, int4_gemm_tc_kernel<64>, tmAct, tmW, p, (const __half *)scales, group, m_base, n_inst);
         } else {
             cfg.dynamicSmemBytes = Cfg<128>::SMEM_BYTES + sc_bytes;
-            e = cudaLaunchKernelEx(&cfg, int4_gemm_tc_kernel<128>, tmAct, tmW, p, (const __half *)scales, group, m_base);
+            e = cudaLaunchKernelEx(&cfg, int4_gemm_tc_kernel<128>, tmAct, tmW, p, (const __half *)scales, group, m_base, n_inst);
         }
         rc = check_cuda(e, "int4 tensor-core matmul launch");
         if (rc) return rc;
