@@ -257,32 +257,33 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            // UMMA N = the activation rows of this pass rounded up to 16: the tensor pipe's time per instruction grows
-            // with N, and it is shared with the SM's other CTA.
-            const uint32_t idesc = make_idesc(0u /*F16*/, false, false, BW, (uint32_t)n_inst);
-            int ws = 0;
-            uint32_t wphase = 0;
-            bool ok = true;
-            for (int i = 0; i < n_units; ++i) {
-                // One wait per unit: the first dequantising warp of the unit's group has seen the unit's activations
-                // arrive before it reports its rows (below), so this barrier covers both operands.
-                if (!mbar_wait_short(smem_u32(&bar_w_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t w0 = tmem_base + (uint32_t)(MB + ws * W_COLS), a0 = act_ring + ws * C::ACT_BYTES;
+        // The whole warp walks the loop and keeps addresses and descriptors warp-uniform; one elected lane issues.
+        // UMMA N = the activation rows of this pass rounded up to 16.
+        const uint32_t idesc = make_idesc(0u /*F16*/, false, false, BW, (uint32_t)n_inst);
+        const uint64_t desc0 = make_smem_desc_sw128(act_ring, 16, 1024);
+        int ws = 0;
+        uint32_t wphase = 0;
+        bool ok = true;
+        for (int i = 0; i < n_units; ++i) {
+            // One wait per unit: the first dequantising warp of the unit's group has seen the unit's activations
+            // arrive before it reports its rows (below), so this barrier covers both operands.
+            ok = mbar_wait_short_warp(smem_u32(&bar_w_full[ws]), wphase, &abort_flag, p.status, WAIT_MMA_FULL);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t w0 = tmem_base + (uint32_t)(MB + ws * W_COLS);
+            const uint64_t d0 = desc0 + (uint64_t)((uint32_t)(ws * C::ACT_BYTES) >> 4); // the start-address field counts 16 bytes
+            if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint64_t ad = make_smem_desc_sw128(a0 + (ks >> 2) * C::ACT_HALF + (ks & 3) * 32, 16, 1024);
-                    umma_a_tmem(tmem_base, w0 + (uint32_t)(ks * 8), ad, idesc, (i | ks) ? 1u : 0u);
-                }
+                for (int ks = 0; ks < 8; ++ks)
+                    umma_a_tmem(tmem_base, w0 + (uint32_t)(ks * 8), d0 + (uint64_t)(((ks >> 2) * C::ACT_HALF + (ks & 3) * 32) >> 4), idesc,
+                                (i | ks) ? 1u : 0u);
                 umma_commit(smem_u32(&bar_w_empty[ws])); // the unit in tensor memory and its activations are free
-                if (++ws == W_STAGES) { ws = 0; wphase ^= 1u; }
             }
-            if (ok) umma_commit(smem_u32(&bar_acc_full));
+            __syncwarp();
+            if (++ws == W_STAGES) { ws = 0; wphase ^= 1u; }
         }
+        if (ok && elect_one()) umma_commit(smem_u32(&bar_acc_full));
+        __syncwarp();
     } else {
         // ------------------------------------------------------------ dequantise (warps 3..10)
         // Thread = weight row; warps 3..6 take the even units of the CTA's walk, warps 7..10 the odd ones, each
