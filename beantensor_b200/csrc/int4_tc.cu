@@ -146,12 +146,14 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     const int n0 = tile * BW;
     // This CTA's K slice, in 128-k units; every CTA starts its walk at a different unit of the slice: CTAs of
     // the same rank read the same activations and in lock step would all ask the same L2 lines at once.
+    // (Everything here is on every thread's way to its first useful instruction: 32-bit unsigned divisions only.)
+    const uint32_t ugroup = (uint32_t)group;
     const int units = p.K / UNIT_K;
-    const int u0 = (int)((long long)units * crank / csize), u1 = (int)((long long)units * (crank + 1) / csize);
+    const int u0 = (int)((uint32_t)units * crank / csize), u1 = (int)((uint32_t)units * (crank + 1u) / csize);
     const int n_units = u1 - u0;
-    const int u_first = n_units > 0 ? tile % n_units : 0;
-    const int g_first = (u0 * UNIT_K) / group;
-    const int g_cnt = n_units > 0 ? (u1 * UNIT_K - 1) / group - g_first + 1 : 0;
+    const int u_first = n_units > 0 ? (int)((uint32_t)tile % (uint32_t)n_units) : 0;
+    const int g_first = (int)((uint32_t)(u0 * UNIT_K) / ugroup);
+    const int g_cnt = n_units > 0 ? (int)((uint32_t)(u1 * UNIT_K - 1) / ugroup) - g_first + 1 : 0;
     // i-th unit of this CTA's walk
     auto unit_at = [&](int i) {
         int u = u_first + i;
@@ -159,12 +161,36 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
         return u + u0;
     };
 
+    // Programmatic dependent launch: this grid lets its successor on the stream start as soon as the machine has
+    // room for its CTAs. Weights and scales are constants, so a CTA may fetch them while its predecessor still runs;
+    // the activations are read and the output is written only after griddepcontrol.wait (warp 2 and the epilogue).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == 0 && lane == 0) {
+        // The first weight units are requested before anything else in the CTA is set up: they come from HBM
+        // and everything downstream waits for them.
+        for (int i = 0; i < RAW_STAGES; ++i) mbar_init(smem_u32(&bar_raw_full[i]), 1);
+        fence_mbar_init();
+        for (int i = 0; i < RAW_STAGES && i < n_units; ++i) {
+            mbar_expect_tx(smem_u32(&bar_raw_full[i]), RAW_BYTES);
+            tma_load_3d(raw_ring + i * RAW_BYTES, &tmW, unit_at(i) * (UNIT_K / 2), n0, 0, smem_u32(&bar_raw_full[i]));
+        }
+        abort_flag = 0;
+        for (int i = 0; i < RAW_STAGES; ++i) mbar_init(smem_u32(&bar_raw_empty[i]), 4);
+        for (int i = 0; i < W_STAGES; ++i) {
+            mbar_init(smem_u32(&bar_act_full[i]), 1);
+            mbar_init(smem_u32(&bar_w_full[i]), 4);
+            mbar_init(smem_u32(&bar_w_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&bar_acc_full), 1);
+        fence_mbar_init();
+    }
     // The dequantising warps ask for their slice's scales before anything else happens in the CTA: once the weight
     // ring's first loads are queued (a dozen megabytes over the whole grid) a small load comes back microseconds
     // later, and no weight can be dequantised before the scales are there.
     constexpr int SC_PRE = 6; // per-thread prefetch depth; the rest (long K or small groups) is fetched afterwards
     __half sc_pre[SC_PRE];
-    const int sc_total = BW * g_cnt, G = p.K / group;
+    const int sc_total = BW * g_cnt, G = (int)((uint32_t)p.K / ugroup);
 #ifndef BTM_I4TC_SCALES_DIRECT
 #define BTM_I4TC_SCALES_DIRECT 0
 #endif
@@ -180,42 +206,19 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             sd1 = __ldg(grow + (u * UNIT_K + BKE) / group);
         }
     }
-    if (!BTM_I4TC_SCALES_DIRECT && warp >= 3) {
+    if (!BTM_I4TC_SCALES_DIRECT && warp >= 3 && g_cnt > 0) {
+        // element i = r * g_cnt + g of the slice's scales; one division, then steps of 256 elements
+        const uint32_t i0 = threadIdx.x - DQ_FIRST, gc = (uint32_t)g_cnt, rstep = 256u / gc, gstep = 256u - rstep * gc;
+        uint32_t r = i0 / gc, g = i0 - r * gc;
 #pragma unroll
         for (int j = 0; j < SC_PRE; ++j) {
-            const int i = (int)threadIdx.x - DQ_FIRST + j * 256;
-            if (i < sc_total) {
-                const int r = i / g_cnt, g = i - r * g_cnt;
-                sc_pre[j] = __ldg(scales + (size_t)min(n0 + r, p.N - 1) * G + g_first + g);
-            }
+            if ((int)i0 + j * 256 < sc_total) sc_pre[j] = __ldg(scales + (size_t)min(n0 + (int)r, p.N - 1) * G + g_first + (int)g);
+            r += rstep;
+            g += gstep;
+            if (g >= gc) { g -= gc; ++r; }
         }
     }
 
-    // Programmatic dependent launch: this grid lets its successor on the stream start as soon as the machine has
-    // room for its CTAs. Weights and scales are constants, so a CTA may fetch them while its predecessor still runs;
-    // the activations are read and the output is written only after griddepcontrol.wait (warp 2 and the epilogue).
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    if (warp == 0 && lane == 0) {
-        abort_flag = 0;
-        for (int i = 0; i < RAW_STAGES; ++i) {
-            mbar_init(smem_u32(&bar_raw_full[i]), 1);
-            mbar_init(smem_u32(&bar_raw_empty[i]), 4);
-        }
-        for (int i = 0; i < W_STAGES; ++i) {
-            mbar_init(smem_u32(&bar_act_full[i]), 1);
-            mbar_init(smem_u32(&bar_w_full[i]), 4);
-            mbar_init(smem_u32(&bar_w_empty[i]), 1);
-        }
-        mbar_init(smem_u32(&bar_acc_full), 1);
-        fence_mbar_init();
-        // The first weight units are requested before anything else in the CTA is set up: they come from HBM
-        // and everything downstream waits for them.
-        for (int i = 0; i < RAW_STAGES && i < n_units; ++i) {
-            mbar_expect_tx(smem_u32(&bar_raw_full[i]), RAW_BYTES);
-            tma_load_3d(raw_ring + i * RAW_BYTES, &tmW, unit_at(i) * (UNIT_K / 2), n0, 0, smem_u32(&bar_raw_full[i]));
-        }
-    }
     if (warp == 1) {
         tmem_alloc<1>(smem_u32(&tmem_base_holder), TMEM_COLS);
         tmem_relinquish<1>();
