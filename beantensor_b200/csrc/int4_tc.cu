@@ -403,35 +403,46 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     }
     cluster_sync_all(); // every accumulator of the cluster is parked and visible (release / acquire)
     if (epi) asm volatile("griddepcontrol.wait;" ::: "memory"); // long since true; orders this grid's stores behind the predecessor
-    const int t = threadIdx.x - DQ_FIRST, row = t & (BW - 1), half = t >> 7;
+    const int t = threadIdx.x - DQ_FIRST;
     const int per = (((valid + 7) >> 3) + (int)csize - 1) / (int)csize * 8; // columns per CTA, a multiple of 8
     const int c_lo = min(valid, (int)crank * per), c_hi = min(valid, c_lo + per);
     uint16_t *tile_out = reinterpret_cast<uint16_t *>(smem_al + MB * BW * 4); // fp16 [column][128 n] behind the parked values
     if (epi && acc_ok) {
+        // A thread sums four consecutive weight rows of every eighth column: 16-byte loads, a warp reads one whole
+        // parked column (512 bytes) per load, and all loads of a batch are in flight before the first sum.
+        const int r4 = (t & 31) * 4, cw = t >> 5;
         uint32_t src[MAX_SPLIT];
 #pragma unroll
-        for (int r = 0; r < MAX_SPLIT; ++r) src[r] = map_to_cta(smem_base + (uint32_t)row * 4u, (uint32_t)(r < (int)csize ? r : 0));
-        // Twelve columns per thread and batch: with a K split of three all of a thread's 36 remote and local loads
-        // are in flight at once (one round trip over the cluster's shared memory instead of three).
-        constexpr int CB = 12;
+        for (int r = 0; r < MAX_SPLIT; ++r) src[r] = map_to_cta(smem_base + (uint32_t)r4 * 4u, (uint32_t)(r < (int)csize ? r : 0));
+        constexpr int CB = 4;
 #pragma unroll 1
-        for (int c0 = c_lo + half; c0 < c_hi; c0 += 2 * CB) {
-            float x[CB][MAX_SPLIT];
+        for (int c0 = c_lo + cw; c0 < c_hi; c0 += 8 * CB) {
+            float4 x[CB][MAX_SPLIT];
 #pragma unroll
             for (int j = 0; j < CB; ++j) {
-                const uint32_t off = (uint32_t)(c0 + 2 * j) * (BW * 4);
+                const uint32_t off = (uint32_t)(c0 + 8 * j) * (BW * 4);
 #pragma unroll
                 for (int r = 0; r < MAX_SPLIT; ++r)
-                    if (c0 + 2 * j < c_hi && r < (int)csize) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x[j][r]) : "r"(src[r] + off));
+                    if (c0 + 8 * j < c_hi && r < (int)csize)
+                        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                     : "=f"(x[j][r].x), "=f"(x[j][r].y), "=f"(x[j][r].z), "=f"(x[j][r].w)
+                                     : "r"(src[r] + off));
             }
 #pragma unroll
             for (int j = 0; j < CB; ++j) {
-                if (c0 + 2 * j < c_hi) {
-                    float acc = x[j][0];
+                if (c0 + 8 * j < c_hi) {
+                    float4 acc = x[j][0]; // rank order: the sum does not depend on who adds or when
 #pragma unroll
                     for (int r = 1; r < MAX_SPLIT; ++r)
-                        if (r < (int)csize) acc += x[j][r];
-                    tile_out[(c0 + 2 * j - c_lo) * BW + row] = __half_as_ushort(__float2half_rn(acc));
+                        if (r < (int)csize) {
+                            acc.x += x[j][r].x;
+                            acc.y += x[j][r].y;
+                            acc.z += x[j][r].z;
+                            acc.w += x[j][r].w;
+                        }
+                    const __half2 h01 = __floats2half2_rn(acc.x, acc.y), h23 = __floats2half2_rn(acc.z, acc.w);
+                    *reinterpret_cast<uint2 *>(tile_out + (c0 + 8 * j - c_lo) * BW + r4) =
+                        make_uint2(*reinterpret_cast<const uint32_t *>(&h01), *reinterpret_cast<const uint32_t *>(&h23));
                 }
             }
         }
