@@ -202,12 +202,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     tc_fence_after();
                     const int nsub = min(KPS, p.num_kb - kb);
+                    // One descriptor pair per stage; a k-block or k-step only moves the start-address field (which
+                    // counts 16 bytes), so every further descriptor is one addition.
+                    const uint64_t ad0 = make_smem_desc_sw128(smem_base + stage * STAGE_BYTES, 16, 1024);
+                    const uint64_t bd0 = make_smem_desc_sw128(smem_base + stage * STAGE_BYTES + A_BYTES, CHUNK_BYTES, 1024);
                     for (int sub = 0; sub < nsub; ++sub) {
-                        const uint32_t a0 = smem_base + stage * STAGE_BYTES + sub * KB_BYTES, b0 = a0 + A_BYTES;
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) {
-                            const uint64_t ad = make_smem_desc_sw128(a0 + ks * 32, 16, 1024);
-                            const uint64_t bd = make_smem_desc_sw128(b0 + ks * 16 * 128, CHUNK_BYTES, 1024);
+                            const uint64_t ad = ad0 + (uint64_t)((sub * KB_BYTES + ks * 32) >> 4);
+                            const uint64_t bd = bd0 + (uint64_t)((sub * KB_BYTES + ks * 16 * 128) >> 4);
                             umma<2, false>(d_tmem, ad, bd, idesc, (uint32_t)((kb | sub | ks) != 0));
                         }
                     }

@@ -449,7 +449,9 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
     }
     // This thread has read what it needs of the other CTAs' shared memory: tell them now and wait for them at the
     // very end, so that the conversion barrier and the global stores do not sit in front of anybody's exit.
-    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    // (relaxed: the arrival publishes nothing, it only says that this thread's loads have returned, which they
+    // have, their values having been summed.)
+    asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
     if (epi && acc_ok) {
         uint16_t *out = reinterpret_cast<uint16_t *>(p.C[0]);
         const bool vec_store = (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
