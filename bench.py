@@ -45,6 +45,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 NCU_TRAFFIC = {
     "gemm_f16_4096": 105.9e6,  # 89.0 MB read + 16.9 MB written
     "int4_gemv_m1": 23.3e6,    # read; nothing is written back within the kernel
+    "int4_gemm_tc_m64": 23.8e6,  # read; the 1.4 MB of output stay in L2
 }
 
 
@@ -414,8 +415,8 @@ def bench_int4(torch, ops, peaks, M, steps, warmup):
             "algorithmic_bytes": algo, "value": gbs, "unit": "GB/s",
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs / peaks["hbm_gbs"], "frac_nominal": gbs / NOMINAL_HBM_GBS,
-                         "traffic": NCU_TRAFFIC["int4_gemv_m1"] if M == 1 else None,
-                         "traffic_source": "ncu capture of a separate run" if M == 1 else None},
+                         "traffic": NCU_TRAFFIC["int4_gemv_m1"] if M == 1 else NCU_TRAFFIC["int4_gemm_tc_m64"] if M == 64 else None,
+                         "traffic_source": "ncu capture of a separate run" if M in (1, 64) else None},
             "l2": f"{sets} rotating weight copies ({sets * w_bytes >> 20} MiB > L2)"}
 
 

@@ -203,10 +203,10 @@ int btm_bmm(int device, void *stream, int dtype, int batch, int M, int N, int K,
  * groups, rounded to nearest even (for M > 8 the weights are first rounded to fp16 as
  * btm_int4_dequant defines them and the product accumulates in fp32). K % group == 0,
  * group % 32 == 0, K % 32 == 0.
- * Ordering: products with M <= 8 use programmatic dependent launch. If the preceding kernel on the
- * stream is another such product, this one may read w_packed and scales_f16 while that kernel is
- * still running (act_f16 is read and out_f16 written only after it has completed); w_packed and
- * scales_f16 must therefore not be the output of an immediately preceding M <= 8 product. */
+ * Ordering: the products use programmatic dependent launch. If the preceding kernel on the
+ * stream is another int4 product of this library, this one may read w_packed and scales_f16 while
+ * that kernel is still running (act_f16 is read and out_f16 written only after it has completed);
+ * w_packed and scales_f16 must therefore not be the output of an immediately preceding int4 product. */
 int btm_int4_matmul(int device, void *stream, int M, int N, int K, int group, const void *act_f16,
                     const void *w_packed, const void *scales_f16, void *out_f16);
 

@@ -161,3 +161,38 @@ def test_seeded_shape_walk(btm, oracle, case):
     btm.check_device_status(0)
     ref = oracle.int4_matmul(act.view(np.uint16), packed, s.view(np.uint16), group)
     assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, ref) <= 2e-3
+
+
+@pytest.mark.parametrize("M", [4, 32, 64])
+def test_chained_products_order(btm, oracle, M):
+    # The int4 products start early under their predecessor (programmatic dependent launch) and may prefetch weights
+    # and scales, but activations are read and outputs written only after the predecessor has completed. A chain
+    # whose second product consumes the first one's output, launched back to back many times, must give bit for bit
+    # what the same chain gives with a synchronisation after every launch.
+    import torch
+    N1, K1, group = 1024, 1024, 128
+    N2 = 768
+    _, p1, s1, act = make(M, N1, K1, group, 501 + M)
+    _, p2, s2, _ = make(M, N2, N1, group, 502 + M)
+    a = torch.from_numpy(act).cuda()
+    w1, sc1 = torch.from_numpy(p1).cuda(), torch.from_numpy(s1).cuda()
+    w2, sc2 = torch.from_numpy(p2).cuda(), torch.from_numpy(s2).cuda()
+    mid = torch.zeros((M, N1), dtype=torch.float16, device="cuda")
+    out = torch.zeros((M, N2), dtype=torch.float16, device="cuda")
+    btm.matmul_int4_gpu(a, w1, sc1, mid, group)
+    torch.cuda.synchronize()
+    btm.matmul_int4_gpu(mid, w2, sc2, out, group)
+    torch.cuda.synchronize()
+    want_mid, want_out = mid.clone(), out.clone()
+    ref = oracle.int4_matmul(want_mid.cpu().numpy().view(np.uint16), p2, s2.view(np.uint16), group)
+    assert oracle.rel_frobenius(want_out.cpu().numpy().view(np.uint16), oracle.F16, ref) <= 2e-3
+    for _ in range(30):
+        mid.zero_()
+        out.zero_()
+        for _ in range(4):
+            btm.matmul_int4_gpu(a, w1, sc1, mid, group)
+            btm.matmul_int4_gpu(mid, w2, sc2, out, group)
+        torch.cuda.synchronize()
+        assert torch.equal(mid, want_mid)
+        assert torch.equal(out, want_out)
+    btm.check_device_status(0)
