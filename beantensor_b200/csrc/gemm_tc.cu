@@ -14,6 +14,8 @@
 // N-contiguous 128-byte chunks and consumed as an MN-major operand; no transpose pass exists.
 // fp32 inputs run as a three-term TF32 split: z = 0/1 of the tensor maps select the hi and lo
 // planes prepared by split_tf32_kernel and each k-step issues hi.hi, hi.lo and lo.hi.
+#include <cstring>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -141,6 +143,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // The fp32 product is launched with programmatic stream serialisation behind the pass that writes its
+            // operand planes: everything up to here (barriers, tensor memory, descriptor prefetch) ran under that
+            // pass; the planes are read only now. Every other role depends on these loads through the stage barriers.
+            if constexpr (Cfg::kTf32) asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const TileCoord tc = decode_tile<BN>(p, tile);
                 for (int kb = 0; kb < p.num_kb; kb += Cfg::kKps) {
@@ -207,24 +213,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     tc_fence_after();
                     const int nsub = min(Cfg::kKps, p.num_kb - kb);
+                    // One descriptor per operand plane and stage; a k-block or a k-step only moves the start-address
+                    // field (it counts 16 bytes), so every further descriptor is one addition instead of a rebuild.
+                    // A: K-major, 8-row groups 1024 B apart; a k-step moves 32 B inside the swizzle span.
+                    // B: MN-major, n-chunks kChunkBytes apart (leading offset), 8-k-row groups 1024 B
+                    // apart (stride offset); a k-step moves kUmmaKRows rows of 128 B.
+                    const uint32_t a0 = smem_base + stage * Cfg::kStageBytes, b0 = a0 + Cfg::kPlanes * Cfg::kABytes;
+                    const uint64_t a_hi0 = Cfg::kAMnMajor ? make_smem_desc_sw128(a0, Cfg::kChunkBytes, 1024) : make_smem_desc_sw128(a0, 16, 1024);
+                    const uint64_t b_hi0 = Cfg::kBMnMajor ? make_smem_desc_sw128(b0, Cfg::kChunkBytes, 1024) : make_smem_desc_sw128(b0, 16, 1024);
+                    constexpr uint32_t a_step = (Cfg::kAMnMajor ? Cfg::kUmmaKRows * SLICE_BYTES : UMMA_K_BYTES) >> 4;
+                    constexpr uint32_t b_step = (Cfg::kBMnMajor ? Cfg::kUmmaKRows * SLICE_BYTES : UMMA_K_BYTES) >> 4;
                     for (int sub = 0; sub < nsub; ++sub) {
-                        const uint32_t sbase = smem_base + stage * Cfg::kStageBytes + sub * Cfg::kKbBytes;
-                        const uint32_t a0 = sbase, b0 = sbase + Cfg::kPlanes * Cfg::kABytes;
+                        const uint32_t sub_off = (uint32_t)(sub * Cfg::kKbBytes) >> 4;
 #pragma unroll
                         for (int ks = 0; ks < Cfg::kKSteps; ++ks) {
-                            // A: K-major, 8-row groups 1024 B apart; a k-step moves 32 B inside the swizzle span.
-                            // B: MN-major, n-chunks kChunkBytes apart (leading offset), 8-k-row groups 1024 B
-                            // apart (stride offset); a k-step moves kUmmaKRows rows of 128 B.
-                            const uint64_t a_hi = Cfg::kAMnMajor
-                                                      ? make_smem_desc_sw128(a0 + ks * Cfg::kUmmaKRows * SLICE_BYTES, Cfg::kChunkBytes, 1024)
-                                                      : make_smem_desc_sw128(a0 + ks * UMMA_K_BYTES, 16, 1024);
-                            const uint64_t b_hi = Cfg::kBMnMajor
-                                                      ? make_smem_desc_sw128(b0 + ks * Cfg::kUmmaKRows * SLICE_BYTES, Cfg::kChunkBytes, 1024)
-                                                      : make_smem_desc_sw128(b0 + ks * UMMA_K_BYTES, 16, 1024);
+                            const uint64_t a_hi = a_hi0 + (uint64_t)(sub_off + ks * a_step);
+                            const uint64_t b_hi = b_hi0 + (uint64_t)(sub_off + ks * b_step);
                             const uint32_t first = (kb | sub | ks) != 0;
                             if constexpr (Cfg::kTf32) {
-                                const uint64_t a_lo = make_smem_desc_sw128(a0 + Cfg::kABytes + ks * UMMA_K_BYTES, 16, 1024);
-                                const uint64_t b_lo = make_smem_desc_sw128(b0 + Cfg::kBBytes + ks * UMMA_K_BYTES, 16, 1024);
+                                // the low planes lie kABytes / kBBytes behind the high ones, K-major like them
+                                const uint64_t a_lo = a_hi + (uint64_t)(Cfg::kABytes >> 4);
+                                const uint64_t b_lo = b_hi + (uint64_t)(Cfg::kBBytes >> 4);
                                 umma<1, true>(d_tmem, a_lo, b_hi, idesc, first);
                                 umma<1, true>(d_tmem, a_hi, b_lo, idesc, 1u);
                                 umma<1, true>(d_tmem, a_hi, b_hi, idesc, 1u);
@@ -291,6 +300,7 @@ __global__ void split_tf32_kernel(const float *__restrict__ src, long long ld, i
                                   float *__restrict__ hi, float *__restrict__ lo, long long ld_dst)
 {
     const long long total = (long long)rows * ld_dst;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); // the product behind this pass may set itself up now
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / ld_dst;
         const int c = (int)(i - r * ld_dst);
@@ -308,6 +318,7 @@ __global__ void split_tf32_transpose_kernel(const float *__restrict__ src, long 
 {
     __shared__ float tile[32][33];
     const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int i = threadIdx.y; i < 32; i += blockDim.y) {
         const int r = r0 + i, c = c0 + threadIdx.x;
         tile[i][threadIdx.x] = (r < rows && c < cols) ? src[(long long)r * ld + c] : 0.0f;
@@ -332,6 +343,7 @@ __global__ void split_tf32_pair_kernel(const float *__restrict__ A, long long ld
 {
     __shared__ float tile[32][33];
     const int blk = blockIdx.x;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); // the product behind this pass may set itself up now
     if (blk < tiles_a) {
         const int r0 = (blk / kt) * 32, c0 = (blk % kt) * 32;
         for (int i = threadIdx.y; i < 32; i += blockDim.y) {
@@ -417,6 +429,21 @@ static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, con
     p.tiles_tail = 2 * tail_big;
     const long long sched = (long long)p.tiles_full + p.tiles_tail;
     const int grid = (int)(sched < sm_count ? sched : sm_count);
+    if constexpr (DT == BTM_F32) {
+        // Behind the split pass on the same stream: start early, read the planes after griddepcontrol.wait.
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)grid, 1, 1);
+        cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        return check_cuda(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, DT, BT, AT>, tmA, tmB, cm, p), "gemm_tc launch");
+    }
     gemm_tc_kernel<BN, DT, BT, AT><<<grid, NUM_THREADS, Cfg::kSmemBytes, st>>>(tmA, tmB, cm, p);
     return check_cuda(cudaGetLastError(), "gemm_tc launch");
 }
