@@ -114,6 +114,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u; // swizzle atoms need 1024-byte alignment
     const int total_tiles = p.tiles_full + p.tiles_tail;
 
+    // Programmatic dependent launch: a product that follows this one on the stream may become resident wherever an
+    // SM falls free and set itself up; it reads its operands (and so writes its output) only after this grid has
+    // completed (griddepcontrol.wait in its producer).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < Cfg::kStages; ++s) {
@@ -143,10 +147,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            // The fp32 product is launched with programmatic stream serialisation behind the pass that writes its
-            // operand planes: everything up to here (barriers, tensor memory, descriptor prefetch) ran under that
-            // pass; the planes are read only now. Every other role depends on these loads through the stage barriers.
-            if constexpr (Cfg::kTf32) asm volatile("griddepcontrol.wait;" ::: "memory");
+            // The product is launched with programmatic stream serialisation: everything up to here (barriers,
+            // tensor memory, descriptor prefetch) may have run under its predecessor (for fp32, the pass that writes
+            // the operand planes); the operands are read only now. Every other role, the stores of C included,
+            // depends on these loads through the stage barriers.
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const TileCoord tc = decode_tile<BN>(p, tile);
                 for (int kb = 0; kb < p.num_kb; kb += Cfg::kKps) {
@@ -429,8 +434,7 @@ static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, con
     p.tiles_tail = 2 * tail_big;
     const long long sched = (long long)p.tiles_full + p.tiles_tail;
     const int grid = (int)(sched < sm_count ? sched : sm_count);
-    if constexpr (DT == BTM_F32) {
-        // Behind the split pass on the same stream: start early, read the planes after griddepcontrol.wait.
+    {
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3((unsigned)grid, 1, 1);
@@ -444,8 +448,6 @@ static int launch_one(cudaStream_t st, int sm_count, const CUtensorMap &tmA, con
         cfg.numAttrs = 1;
         return check_cuda(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, DT, BT, AT>, tmA, tmB, cm, p), "gemm_tc launch");
     }
-    gemm_tc_kernel<BN, DT, BT, AT><<<grid, NUM_THREADS, Cfg::kSmemBytes, st>>>(tmA, tmB, cm, p);
-    return check_cuda(cudaGetLastError(), "gemm_tc launch");
 }
 
 template <int BN, int DT, bool BT = false, bool AT = false>

@@ -19,6 +19,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 #include "btm_internal.h"
 #include "btm_ptx.cuh"
@@ -119,6 +120,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int total_tiles = p.tiles_full + p.tiles_tail;
 
+    // Programmatic dependent launch: a product that follows this one on the stream may become resident wherever an
+    // SM pair falls free and set itself up; it reads its operands (and so writes its output) only after this grid
+    // has completed (griddepcontrol.wait in its producers).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
@@ -149,6 +154,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // The operands may be the predecessor's output. Every other role, the stores of C included, depends on
+            // these loads through the stage barriers.
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters) {
                 const PairTile pt = decode_pair_tile(p, tile);
                 const int half_bn = pt.bn >> 1;      // columns of B this CTA loads
@@ -307,8 +315,18 @@ static int launch_pair(cudaStream_t st, int sm_count, const CUtensorMap &tmA, co
     p.tiles_tail = 2 * tail_big;
     const long long sched = (long long)p.tiles_full + p.tiles_tail;
     const int clusters = (int)(sched < max_clusters ? sched : max_clusters);
-    gemm_tc2_kernel<DT><<<2 * clusters, THREADS, SMEM_BYTES, st>>>(tmA, tmB, cm, p);
-    return check_cuda(cudaGetLastError(), "gemm_tc2 launch");
+    cudaLaunchConfig_t lc;
+    memset(&lc, 0, sizeof(lc));
+    lc.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+    lc.blockDim = dim3(THREADS, 1, 1);
+    lc.dynamicSmemBytes = SMEM_BYTES;
+    lc.stream = st;
+    cudaLaunchAttribute pdl;
+    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization; // the kernel orders itself with griddepcontrol
+    pdl.val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = &pdl;
+    lc.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&lc, gemm_tc2_kernel<DT>, tmA, tmB, cm, p), "gemm_tc2 launch");
 }
 
 int configure_gemm_tc2_kernels()
