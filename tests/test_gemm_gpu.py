@@ -344,3 +344,48 @@ def test_transposed_and_strided_operands_without_a_copy(btm, oracle, dtype, layo
         btm.check_device_status(0)
         err = oracle.rel_frobenius(to_host_bits(out, dtype), dtype, oracle.gemm(dtype, A, B))
         assert err <= TOL[dtype], (layout, (M, N, K), err)
+
+
+@pytest.mark.parametrize("kind", ["1cta", "2cta", "fp32"])
+def test_chained_products_order(btm, kind, monkeypatch):
+    # The products are launched with programmatic stream serialisation: a product may become resident and set itself up
+    # while its predecessor still runs, but it reads its operands and writes its output only after the predecessor has
+    # completed. A chain C1 = A.B1, C2 = C1.B2, A' = C2 (the next round's output lands in a buffer the chain reads),
+    # launched back to back many times, must give bit for bit what it gives with a synchronisation after every launch.
+    import torch
+    if kind != "fp32":
+        monkeypatch.setenv("BTM_FORCE_KERNEL", kind)
+    dt = torch.float32 if kind == "fp32" else torch.float16
+    n = 768
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = (torch.rand((n, n), device="cuda", generator=g) - 0.5).to(dt)
+    b1 = (torch.rand((n, n), device="cuda", generator=g) * (2.0 / n ** 0.5)).to(dt)
+    b2 = (torch.rand((n, n), device="cuda", generator=g) * (2.0 / n ** 0.5)).to(dt)
+    c1, c2, c3 = (torch.zeros((n, n), device="cuda", dtype=dt) for _ in range(3))
+
+    def chain(sync):
+        for buf in (c1, c2, c3):
+            buf.zero_()
+        for _ in range(3):
+            btm.matmul_gpu(a, b1, c1)
+            if sync:
+                torch.cuda.synchronize()
+            btm.matmul_gpu(c1, b2, c2)
+            if sync:
+                torch.cuda.synchronize()
+            btm.matmul_gpu(c2, b1, c3)  # reads what the previous launch wrote ...
+            if sync:
+                torch.cuda.synchronize()
+            btm.matmul_gpu(c3, b2, c1)  # ... and overwrites a buffer an earlier launch of the chain read
+            if sync:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        return c1.clone(), c2.clone(), c3.clone()
+
+    want = chain(sync=True)
+    assert all(torch.isfinite(w).all() for w in want)
+    for _ in range(20):
+        got = chain(sync=False)
+        for w, x in zip(want, got):
+            assert torch.equal(w, x)
+    btm.check_device_status(0)
