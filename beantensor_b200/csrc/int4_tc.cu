@@ -374,7 +374,7 @@ int4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_w_full[ws]));
         }
-        if (ok) mbar_wait_warp(smem_u32(&bar_acc_full), 0u, &abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+        if (ok) mbar_wait_short_warp(smem_u32(&bar_acc_full), 0u, &abort_flag, p.status, WAIT_EPI_TMEM_FULL); // short polls: the wake-up of a long sleep is on the critical path here
         tc_fence_after();
     }
 
