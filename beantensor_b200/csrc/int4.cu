@@ -19,6 +19,7 @@
 
 #include "btm_internal.h"
 #include "btm_ptx.cuh"
+#include "int4_unpack.cuh"
 
 namespace btm {
 
@@ -706,24 +707,26 @@ __global__ void int4_matmul_general_kernel(int M, int N, int K, int group, const
 __global__ void int4_dequant_kernel(long long nbytes, int K, int group, const uint8_t *__restrict__ w,
                                     const __half *__restrict__ scales, __half *__restrict__ out)
 {
-    // One thread per packed 32-bit word (8 weights) -> one 16-byte store.
+    // One thread per packed 32-bit word (8 weights) -> one 16-byte store; a warp reads 128 and writes 512 contiguous
+    // bytes. Word i lies in row i / (K/8) at k = 8 * (i mod (K/8)); 8 divides the group, so one scale per word.
     const long long words = nbytes / 4;
     const int G = K / group;
+    const uint32_t wpr = (uint32_t)K >> 3, gshift_words = (uint32_t)group >> 3; // words per row, words per group
+    const bool small = words <= 0xFFFFFFFFLL;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < words; i += (long long)gridDim.x * blockDim.x) {
         const uint32_t x = __ldg(reinterpret_cast<const uint32_t *>(w) + i);
-        const long long e0 = i * 8; // first element index
-        const long long n = e0 / K;
-        const int k0 = (int)(e0 - n * K);
-        const float s = __half2float(__ldg(scales + n * G + k0 / group)); // 8 | group: one scale per word
-        uint32_t o[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int lo = (int)(((x >> (8 * j)) & 0xF) ^ 8) - 8;
-            const int hi = (int)(((x >> (8 * j + 4)) & 0xF) ^ 8) - 8;
-            __half2 h = __floats2half2_rn((float)lo * s, (float)hi * s);
-            o[j] = *reinterpret_cast<uint32_t *>(&h);
+        long long n;
+        uint32_t wi; // word index inside the row
+        if (small) { // 32-bit division: the 64-bit one costs more than the rest of the thread's work
+            const uint32_t q = (uint32_t)i / wpr;
+            n = q;
+            wi = (uint32_t)i - q * wpr;
+        } else {
+            n = i / wpr;
+            wi = (uint32_t)(i - n * wpr);
         }
-        reinterpret_cast<uint4 *>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        const __half s = __ldg(scales + n * G + wi / gshift_words);
+        reinterpret_cast<uint4 *>(out)[i] = dequant_word(x, __half2half2(s));
     }
 }
 

@@ -201,8 +201,10 @@ int btm_bmm(int device, void *stream, int dtype, int batch, int M, int N, int K,
  * consecutive k ([N, K/group]). The dtype is this build's addition to Tensor/Dtypes.h:57-70.
  * Arithmetic: fp32 accumulation of act*w inside a group, times the scale, summed over
  * groups, rounded to nearest even (for M > 8 the weights are first rounded to fp16 as
- * btm_int4_dequant defines them and the product accumulates in fp32). K % group == 0,
- * group % 32 == 0, K % 32 == 0.
+ * btm_int4_dequant defines them and the product accumulates in fp32; from 640 rows on those
+ * fp16 weights are written once into stream-ordered scratch of N*K*2 bytes from the library's
+ * per-device pool and multiplied by the dense tensor-core kernel, instead of being unpacked again
+ * for every 128 rows). K % group == 0, group % 32 == 0, K % 32 == 0.
  * Ordering: the products use programmatic dependent launch. If the preceding kernel on the
  * stream is another int4 product of this library, this one may read w_packed and scales_f16 while
  * that kernel is still running (act_f16 is read and out_f16 written only after it has completed);

@@ -196,3 +196,24 @@ def test_chained_products_order(btm, oracle, M):
         assert torch.equal(mid, want_mid)
         assert torch.equal(out, want_out)
     btm.check_device_status(0)
+
+
+@pytest.mark.parametrize("case", [(600, 1088, 1024, 128, None), (1024, 264, 512, 64, None), (40, 64, 4096, 128, "16"), (130, 200, 256, 128, "100"),
+                                  (600, 1088, 1024, 128, "100000")])
+def test_many_rows_take_the_dequantise_once_route(btm, oracle, case, monkeypatch):
+    # From 512 activation rows on the weights are dequantised once into scratch and multiplied by the dense tensor-core
+    # kernel; below, the tcgen05 int4 kernel unpacks them per 128 rows. Both multiply by the btm_int4_dequant values, so
+    # both must agree with a product of exactly those values; the threshold is moved to run small shapes through the
+    # scratch route and a large one through the per-pass kernel.
+    M, N, K, group, threshold = case
+    if threshold:
+        monkeypatch.setenv("BTM_INT4_LARGE_M", threshold)
+    w, packed, s, act = make(M, N, K, group, 77 + M)
+    out = gpu_matmul(btm, act, packed, s, group)
+    btm.check_device_status(0)
+    assert not np.isnan(out).any()
+    ref = oracle.int4_matmul(act.view(np.uint16), packed, s.view(np.uint16), group)
+    assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, ref) <= 2e-3
+    dq = oracle.int4_dequant(packed, s.view(np.uint16), group)
+    ref_dq = oracle.gemm(oracle.F16, act.view(np.uint16), np.ascontiguousarray(dq.T))
+    assert oracle.rel_frobenius(out.view(np.uint16), oracle.F16, ref_dq) <= 5e-4
