@@ -713,20 +713,34 @@ __global__ void int4_dequant_kernel(long long nbytes, int K, int group, const ui
     const int G = K / group;
     const uint32_t wpr = (uint32_t)K >> 3, gshift_words = (uint32_t)group >> 3; // words per row, words per group
     const bool small = words <= 0xFFFFFFFFLL;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < words; i += (long long)gridDim.x * blockDim.x) {
-        const uint32_t x = __ldg(reinterpret_cast<const uint32_t *>(w) + i);
-        long long n;
-        uint32_t wi; // word index inside the row
-        if (small) { // 32-bit division: the 64-bit one costs more than the rest of the thread's work
-            const uint32_t q = (uint32_t)i / wpr;
-            n = q;
-            wi = (uint32_t)i - q * wpr;
-        } else {
-            n = i / wpr;
-            wi = (uint32_t)(i - n * wpr);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    constexpr int UN = 4; // words in flight per thread: one load per thread at a time left the read side latency-bound
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < words; i0 += UN * stride) {
+        uint32_t x[UN];
+        __half sc[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < words) {
+                x[u] = __ldg(reinterpret_cast<const uint32_t *>(w) + i);
+                long long n;
+                uint32_t wi; // word index inside the row
+                if (small) { // 32-bit division: the 64-bit one costs more than the rest of the thread's work
+                    const uint32_t q = (uint32_t)i / wpr;
+                    n = q;
+                    wi = (uint32_t)i - q * wpr;
+                } else {
+                    n = i / wpr;
+                    wi = (uint32_t)(i - n * wpr);
+                }
+                sc[u] = __ldg(scales + n * G + wi / gshift_words);
+            }
         }
-        const __half s = __ldg(scales + n * G + wi / gshift_words);
-        reinterpret_cast<uint4 *>(out)[i] = dequant_word(x, __half2half2(s));
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < words) reinterpret_cast<uint4 *>(out)[i] = dequant_word(x[u], __half2half2(sc[u]));
+        }
     }
 }
 
