@@ -4,8 +4,8 @@
 // fp16 tcgen05 matmul with fp32 accumulation in tensor memory.
 //
 // The product is computed transposed: the 128 dequantised weight rows of a CTA are the tensor core's
-// A operand (its full 128-row datapath), the activation rows are the B operand (UMMA N = 64 or 128), so
-// no tensor-core row is spent on padding when M is small. K is split over the CTAs of a cluster, which
+// A operand (its full 128-row datapath), the activation rows are the B operand (UMMA N = the rows of the
+// pass rounded up to 16), so no tensor-core row is spent on padding when M is small. K is split over the CTAs of a cluster, which
 // puts two or three times as many CTAs on the machine as there are 128-row weight tiles (86 for
 // N = 11008) and divides the activation bytes a CTA pulls from L2 by the same factor; the partial
 // accumulators are summed over the cluster's shared memory, every CTA taking a share of the activation rows.
@@ -19,16 +19,19 @@
 //               the group scale, and write the row's 128 fp16 straight into tensor memory (tcgen05.st,
 //               64 columns of the thread's own lane): the tensor core takes its A operand from
 //               there, so the tile never passes through shared memory and needs no proxy fence. A
-//               warp passes one set of hand-offs per 128 k; those hand-offs, not arithmetic or
-//               bandwidth, are what the kernel's time is made of;
+//               warp passes one set of hand-offs per 128 k. The unpack instructions of these warps
+//               are what the main loop's time is made of (24 issue cycles per 32-bit word);
 //   warp 1      tcgen05.mma (M = 128, N = MB, A from tensor memory, B K-major in shared memory): one wait,
 //               eight MMAs and one tcgen05.commit per unit (the commit frees the unit in tensor memory and
 //               its activations). Its issue is serial and shares the tensor pipe with the SM's other CTA,
-//               so everything else has been moved off this thread.
+//               so everything else has been moved off this warp, and it walks its loop as a whole warp with
+//               warp-uniform descriptors (one elected lane issues).
 // Then every CTA parks its accumulator (lane = weight row, column = activation row) in its own shared
 // memory, and after one cluster barrier CTA r fetches block r of the columns from all CTAs over DSMEM,
 // adds them in rank order, rounds once to fp16, transposes through shared memory and stores rows of 256
 // contiguous bytes of out[m, n0 .. n0 + 128) for its block of m.
+// The kernel is launched with programmatic stream serialisation: weights and scales are fetched while the
+// predecessor on the stream may still run; activations are read and the output written after griddepcontrol.wait.
 // HBM traffic: the packed weights once (N*K/2 bytes) plus scales; activations come from L2
 // (N/128 x M x K x 2 bytes in total, whatever the split).
 #include <cuda_fp16.h>
